@@ -8,7 +8,9 @@ something per request) follow as further entries.
 Paged groups.  Entries that need all keys and entries that need a window of them are
 different groups: each group has its own page pool and its own block table per request,
 so a window group can give pages back as the window passes them while the other keeps
-everything.  Entries that hold one row per run of ``every`` positions (summaries of
+everything.  A window entry that also reads the first positions of a sequence for ever
+(``keep_first``) is a group of its own kind: its tables keep the pages of those positions
+and have their holes between them and the window.  Entries that hold one row per run of ``every`` positions (summaries of
 blocks) form groups of their own as well, with a pool sized for that many fewer rows.  Within a group every entry has its own K and V buffer
 ``[num_pages, page_size, kv_heads, head_dim]`` (widths may differ between entries); a
 page id names the same rows in all of them, as the reference's pages do
@@ -56,10 +58,11 @@ class FixedStateView:
 
 
 class _Group:
-    def __init__(self, index: int, window: Optional[int], every: int, num_pages: int, scratch_pages: int):
+    def __init__(self, index: int, window: Optional[int], every: int, num_pages: int, scratch_pages: int, keep_first: int = 0):
         self.index = index
         self.window = window
         self.every = every
+        self.keep_first = keep_first
         self.num_pages = num_pages
         self.pool = PagePool(num_pages)
         self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))  # behind the pool, held by nobody
@@ -119,11 +122,13 @@ class CacheManager:
                     raise ValueError(f"run entry {pos}: window {need.window} must be positive")
                 if need.every < 1:
                     raise ValueError(f"run entry {pos}: one row per {need.every} positions is not possible")
-                kind = (need.window, need.every)
+                if need.keep_first < 0:
+                    raise ValueError(f"run entry {pos}: {need.keep_first} kept first positions are not possible")
+                kind = (need.window, need.every, need.keep_first if need.window is not None else 0)
                 if kind not in by_kind:
                     # rows per request round down to whole runs, pages round up per request
                     pages = num_pages if need.every == 1 else -(-num_pages // need.every) + num_slots
-                    by_kind[kind] = _Group(len(self.groups), need.window, need.every, pages, scratch_pages)
+                    by_kind[kind] = _Group(len(self.groups), need.window, need.every, pages, scratch_pages, kind[2])
                     self.groups.append(by_kind[kind])
                 group = by_kind[kind]
                 buffer_pages = group.num_pages + scratch_pages
@@ -250,7 +255,7 @@ class CacheManager:
             slot = self.slots.take()  # raises OutOfPages before anything else is taken
             if self.bytes_per_slot:
                 self.state[slot].zero_()
-            held = _Held([BlockTable(self.page_size, g.window, g.every) for g in self.groups], slot)
+            held = _Held([BlockTable(self.page_size, g.window, g.every, g.keep_first) for g in self.groups], slot)
             self._held[request] = held
         for group in self.groups:
             held.tables[group.index].grow(group.pool, held.length + n_tokens)

@@ -84,12 +84,14 @@ HOLE = -1  # a block-table entry whose page went back to the pool (the window pa
 class BlockTable:
     """One request's pages in one group, in position order."""
 
-    def __init__(self, page_size: int, window: int | None = None, every: int = 1):
+    def __init__(self, page_size: int, window: int | None = None, every: int = 1, keep_first: int = 0):
         self.page_size = page_size
         self.window = window
         self.every = every  # one row per complete run of this many positions
         self.pages: list[int] = []
-        self.first_live = 0  # entries below this index are holes
+        # Pages that hold any of the first ``keep_first`` positions stay for the request's life.
+        self.kept = -(-(-(-keep_first // every)) // page_size) if window is not None and keep_first > 0 else 0
+        self.first_live = self.kept  # entries from ``kept`` up to this index are holes
         self._array = np.empty(16, dtype=np.int32)  # the same entries, ready to be copied into a step's table
 
     def pages_for(self, length: int) -> int:
@@ -111,7 +113,7 @@ class BlockTable:
 
     def shrink(self, pool: PagePool, length: int) -> None:
         """Gives back the pages beyond those ``length`` positions need (a claim that was not used)."""
-        keep = max(self.pages_for(length), self.first_live)
+        keep = max(self.pages_for(length), self.first_live if self.first_live > self.kept else 0)
         while len(self.pages) > keep:
             pool.give_back(self.pages.pop())
 
@@ -132,14 +134,14 @@ class BlockTable:
         return released
 
     def release_all(self, pool: PagePool) -> None:
-        for p in self.pages[self.first_live :]:
+        for p in self.live_pages():
             pool.give_back(p)
         self.pages = []
-        self.first_live = 0
+        self.first_live = self.kept
 
     def as_array(self) -> np.ndarray:
         """The entries as int32 (a view; valid until the table grows)."""
         return self._array[: len(self.pages)]
 
     def live_pages(self) -> list[int]:
-        return self.pages[self.first_live :]
+        return self.pages[: self.kept] + self.pages[self.first_live :]

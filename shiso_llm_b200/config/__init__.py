@@ -14,8 +14,10 @@ from .registry import (
 from . import lfm2  # registers Lfm2ForCausalLM
 from . import filulix  # registers Filulix
 from . import zetavik  # registers Zetavik
+from . import volalorn  # registers Volalorn
 from .filulix import FilulixConfig
 from .zetavik import ZetavikConfig
+from .volalorn import VolalornConfig
 from .lfm2 import Lfm2Config, feed_forward_width
 
 __all__ = [
@@ -27,6 +29,7 @@ __all__ = [
     "Lfm2Config",
     "UnknownArchitecture",
     "UnsupportedShape",
+    "VolalornConfig",
     "ZetavikConfig",
     "architecture_of",
     "feed_forward_width",

@@ -259,7 +259,7 @@ SHISO_API int shiso_token_shift_blend(const void* h, int act_dtype, const float*
 
 // --------------------------------------------------------------------------- unary maps
 
-enum { SHISO_UNARY_TANH = 0, SHISO_UNARY_SILU = 1, SHISO_UNARY_RELU2 = 2 };  // relu2: the square of max(x, 0)
+enum { SHISO_UNARY_TANH = 0, SHISO_UNARY_SILU = 1, SHISO_UNARY_RELU2 = 2, SHISO_UNARY_COPY = 3 };  // relu2: the square of max(x, 0); copy: the value in the output's type
 
 template <typename IT, typename OT>
 __global__ void unary_kernel(const IT* __restrict__ x, OT* __restrict__ out, long long count, int kind) {
@@ -269,14 +269,15 @@ __global__ void unary_kernel(const IT* __restrict__ x, OT* __restrict__ out, lon
         float r;
         if (kind == SHISO_UNARY_TANH) r = tanhf(v);
         else if (kind == SHISO_UNARY_SILU) r = v / (1.0f + expf(-v));
-        else r = v > 0.0f ? v * v : 0.0f;
+        else if (kind == SHISO_UNARY_RELU2) r = v > 0.0f ? v * v : 0.0f;
+        else r = v;
         out[i] = from_f32<OT>(r);
     }
 }
 
 SHISO_API int shiso_unary(const void* x, int in_dtype, void* out, int out_dtype, long long count, int kind, cudaStream_t stream) {
     if (count <= 0) return SHISO_OK;
-    if (kind < SHISO_UNARY_TANH || kind > SHISO_UNARY_RELU2) return SHISO_ERR_UNSUPPORTED;
+    if (kind < SHISO_UNARY_TANH || kind > SHISO_UNARY_COPY) return SHISO_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
     if (in_dtype == SHISO_F32 && out_dtype == SHISO_F32)
         launch_kernel(unary_kernel<float, float>, blocks, 256, 0, stream, (const float*)x, (float*)out, count, kind);

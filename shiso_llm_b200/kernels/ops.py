@@ -934,7 +934,7 @@ def token_shift_blend(x, mu, state, step):
     return out
 
 
-_UNARY = {"tanh": 0, "silu": 1, "relu2": 2}
+_UNARY = {"tanh": 0, "silu": 1, "relu2": 2, "copy": 3}  # copy: the values in another element type
 
 
 def unary(x, kind, out_dtype):
@@ -1118,6 +1118,120 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
         _ptr(seen), tokens, heads, kv_heads, dim, vdim, page_size, float(scale), int(window), int(pool), float(out_scale), _stream(),
     )
     _done(status, "pooled_window_attention" + (" (pooled blocks)" if seen is not None else ""), shape=(tokens, heads, dim))
+    return out
+
+
+# --------------------------------------------------------------------------- attention with a parameterised mask and weighting
+
+_HEAD_NORMS = {None: 0, "before": 1, "after": 2}
+_MASKS = {"window": 0, "chunk": 1}
+MASKED_MAX_HEAD_DIM = 256  # what the kernels of this group keep of a head in a warp's registers
+
+
+def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_order, inv_freq, rotary_dim, magnitude, step,
+                       k_cache, v_cache, block_table, page_size, store=True):
+    """Prepares the heads of ``proj[T, heads*dim | kv_heads*dim | kv_heads*vdim | ...]`` in place:
+    an RMS norm over every query and key head (``norm_order`` None, "before" or "after" the
+    rotation; weights ``q_w`` / ``k_w`` of ``[dim]`` or None for a unit norm), the half-split
+    rotation of the first ``rotary_dim`` entries by ``position * inv_freq`` with cosine and sine
+    times ``magnitude``.  Queries are written back where they stood; keys and the values (copied
+    as they are) go to the paged caches.  Returns the query columns."""
+    act = proj.dtype
+    q_cols, k_cols, v_cols = heads * dim, kv_heads * dim, kv_heads * vdim
+    ld = _rows(proj, "projected rows", act)
+    if proj.shape[1] < q_cols + k_cols + v_cols:
+        raise KernelError(f"projected rows of {proj.shape[1]} do not hold {heads} + {kv_heads} heads of {dim} and {kv_heads} of {vdim}")
+    if norm_order not in _HEAD_NORMS:
+        raise KernelError(f"head norm order {norm_order!r}: expected None, 'before' or 'after'")
+    for name, t in (("q norm weight", q_w), ("k norm weight", k_w)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != dim:
+                raise KernelError(f"{name} has {t.shape[0]} entries for heads of {dim}")
+    if rotary_dim:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.shape[0]} entries for a rotation over {rotary_dim}")
+    _check(block_table, "block table", torch.int32, 2)
+    if store:
+        _paged(k_cache, "k cache", act, page_size)
+        _paged(v_cache, "v cache", act, page_size)
+        if k_cache.shape[2:] != (kv_heads, dim) or v_cache.shape[2:] != (kv_heads, vdim):
+            raise KernelError(f"caches of shape {tuple(k_cache.shape)} / {tuple(v_cache.shape)} for {kv_heads} heads of {dim} / {vdim}")
+    status = library().shiso_head_prepare_store(
+        proj.data_ptr(), ld, _CODES[act], 0, q_cols, q_cols + k_cols, _ptr(q_w), _ptr(k_w), _ptr(inv_freq) if rotary_dim else 0,
+        _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1],
+        _ptr(k_cache) if store else 0, _ptr(v_cache) if store else 0, proj.shape[0], heads, kv_heads, dim, vdim, int(rotary_dim),
+        page_size, float(eps), float(magnitude), _HEAD_NORMS[norm_order], int(bool(store)), _stream(),
+    )
+    _done(status, "head_prepare_store", shape=(proj.shape[0], heads + kv_heads, dim))
+    return proj[:, :q_cols]
+
+
+def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
+                     key_bias=None, softcap=None, gate=None):
+    """Attention of every row over the keys its mask shows: ``mask`` "window" (the last ``size``
+    positions and the first ``keep_first`` of the sequence) or "chunk" (the positions of the row's
+    own run of ``size``, counted from 0).  Scores ``(q . k) * scale``, capped as
+    ``softcap * tanh(score / softcap)`` when a cap is given; weights a softmax, or with ``sigmoid``
+    one ``sigmoid(score + key_bias[head])`` per key, not normalised.  ``gate[T, heads]`` (logits)
+    multiplies each head's output by its sigmoid.  ``q`` and ``gate`` may be column ranges.
+    Returns ``[T, heads * vdim]``."""
+    act = q.dtype
+    kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    q_ld = _rows(q, "q", act, heads * dim)
+    _paged(k_cache, "k cache", act, page_size)
+    _paged(v_cache, "v cache", act, page_size)
+    _check(block_table, "block table", torch.int32, 2)
+    if mask not in _MASKS:
+        raise KernelError(f"mask {mask!r}: expected 'window' or 'chunk'")
+    if key_bias is not None:
+        _check(key_bias, "key bias", torch.float32, 1)
+        if key_bias.shape[0] != heads:
+            raise KernelError(f"key bias has {key_bias.shape[0]} entries for {heads} heads")
+    gate_ld = _rows(gate, "gate", act, heads) if gate is not None else 0
+    tokens = q.shape[0]
+    out = torch.empty((tokens, heads * vdim), dtype=act, device=q.device)
+    status = library().shiso_masked_attention(
+        q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+        _ptr(step.seq_of_token), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
+        tokens, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size), int(keep_first),
+        int(bool(sigmoid)), _stream(),
+    )
+    _done(status, f"masked_attention ({mask}, {'sigmoid' if sigmoid else 'softmax'})", shape=(tokens, heads, dim))
+    return out
+
+
+# --------------------------------------------------------------------------- norms on a sublayer's output, polynomial activation
+
+
+def norm_into(residual, y, w, eps, want_rows=True):
+    """``residual += y * rsqrt(mean(y^2) + eps) * w`` (float32 rows, in place); returns the new
+    residual rows in ``y``'s type - the residual itself when that is float32 - or None when not wanted."""
+    _check(residual, "residual", torch.float32, 2)
+    _check(y, "sublayer output", None, 2)
+    _check(w, "norm weight", torch.float32, 1)
+    tokens, hidden = residual.shape
+    if y.shape != residual.shape or w.shape[0] != hidden:
+        raise KernelError(f"output {tuple(y.shape)} and weight {tuple(w.shape)} do not match the residual {tuple(residual.shape)}")
+    out = torch.empty_like(y) if want_rows and y.dtype != torch.float32 else None
+    _done(library().shiso_norm_into(_ptr(residual), _ptr(y), _code(y), _ptr(w), _ptr(out), tokens, hidden, float(eps), _stream()),
+          "norm_into", shape=(tokens, hidden))
+    if not want_rows:
+        return None
+    return residual if out is None else out
+
+
+def polynorm(z, coefficients, eps, out_dtype):
+    """``a N(z) + b N(z^2) + c N(z^3) + e`` per row, ``N(u) = u * rsqrt(mean(u^2) + eps)``;
+    ``coefficients`` = float32 ``[a, b, c, e]``."""
+    ld = _rows(z, "z", out_dtype)
+    _check(coefficients, "coefficients", torch.float32, 1)
+    if coefficients.shape[0] != 4:
+        raise KernelError(f"{coefficients.shape[0]} coefficients where a, b, c and e are expected")
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _done(library().shiso_polynorm(z.data_ptr(), ld, _CODES[out_dtype], _ptr(coefficients), _ptr(out), z.shape[0], z.shape[1], float(eps),
+                                   _stream()), "polynorm", shape=tuple(z.shape))
     return out
 
 

@@ -8,7 +8,7 @@ from .base import (
 )
 from . import norm, position, attention, short_conv, feed_forward, block, embedding  # register built-ins
 from . import hyper, wkv, retention, pooled_attention, parallel  # noqa: F401  (more built-ins)
-from . import lightning, mamba2, latent_attention  # noqa: F401  (more built-ins)
+from . import lightning, mamba2, latent_attention, masked_attention  # noqa: F401  (more built-ins)
 from .model import Model
 
 __all__ = [

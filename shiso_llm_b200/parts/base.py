@@ -50,7 +50,9 @@ class PagedKV:
     than keys (``v_head_dim``; None: the same), and the entry may ask for an element type of
     its own (``dtype``; None: the engine's compute type).  ``every`` > 1 asks for one row per
     complete run of that many positions instead of one per position (summaries of blocks of
-    tokens): a request of ``n`` positions then holds ``n // every`` rows.
+    tokens): a request of ``n`` positions then holds ``n // every`` rows.  ``keep_first`` > 0
+    (with a window) says that the first so many positions are read for the request's whole life:
+    the pages that hold them never go back while the window moves on.
 
     A mixer that needs more than one cache returns a tuple of needs from ``cache_spec`` and
     is handed a tuple of views in the same order."""
@@ -61,6 +63,7 @@ class PagedKV:
     v_head_dim: Optional[int] = None
     dtype: Optional[torch.dtype] = None
     every: int = 1
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -131,6 +134,9 @@ class PositionEncoding(Part):
     # Which two elements of a head form rotation pair i: False - (i, i + rotary_dim/2), the
     # half-split pairing; True - the neighbours (2i, 2i + 1).
     interleaved = False
+    # Cosine and sine of every angle are multiplied by this (1: a plain rotation).  Only kernels
+    # that take a magnitude honour another value; a mixer whose kernels do not must refuse it.
+    magnitude = 1.0
 
     def rotary(self):
         """``(inv_freq, rotary_dim)``: the encoding rotates pair i of every query and key head
@@ -272,6 +278,23 @@ class Stream:
         # output not yet written into the copies: the next read writes it in the same kernel.
         self.lanes: Optional[torch.Tensor] = None
         self.lane_update = None
+        # The residual rows in the compute type, when a kernel that updated the residual also
+        # wrote them out (a layer whose sublayers read the residual itself); dropped by ``add``.
+        self.current: Optional[torch.Tensor] = None
+
+    def rows(self, env) -> torch.Tensor:
+        """The residual rows, up to date, in the compute type of ``env``: what a sublayer that
+        reads the stream itself (no norm before it) is given."""
+        delta = self.take_pending()
+        if delta is not None:
+            for d in delta if isinstance(delta, tuple) else (delta,):
+                self.residual += d.to(self.residual.dtype)
+            self.current = None
+        if env.dtype == torch.float32:
+            return self.residual
+        if self.current is None:
+            self.current = env.ops.unary(self.residual, "copy", env.dtype)
+        return self.current
 
     def lane_values(self) -> Optional[torch.Tensor]:
         """The copies with the waiting update applied, computed on the side (a diagnostic);
@@ -331,6 +354,7 @@ class Stream:
         if self.pending is not None:
             raise RuntimeError("a block output is already waiting to be added to the residual")
         self.pending = delta
+        self.current = None
         if self.observer is not None:
             self.observer(self)
 

@@ -4,6 +4,11 @@
 post-norms (crates/shiso-models/src/lfm2/config.rs:184; the layer loop at
 crates/shiso-engine/src/layers.rs:2003-2294).  A block only marks its outputs as
 pending on the stream; the next norm adds them while it normalises.
+
+``output_norm``: the norm stands behind each sublayer, not before it: ``h = x + norm1(mixer(x))``,
+``x' = h + norm2(ff(h))``; the sublayers read the stream itself.  One kernel per sublayer takes
+the norm of the output, adds it to the float32 residual and writes the new residual out in the
+compute type for the next reader.
 """
 
 from __future__ import annotations
@@ -86,3 +91,51 @@ class ParallelPreNormBlock(Block):
             stream.add(mixed)
         else:
             stream.add((mixed, self.feed_forward.forward(h, step)))
+
+
+@BLOCKS.register("output_norm")
+class OutputNormBlock(Block):
+    """``x <- x + norm(sublayer(x))`` for the mixer and then for the feed-forward (if any)."""
+
+    def __init__(self, spec, env, layer):
+        super().__init__(spec, env)
+        self.name = layer.name
+        self.mixer_norm = NORMS.build(layer.mixer_norm, env)
+        self.mixer = MIXERS.build(layer.mixer, env)
+        self.feed_forward = self.ff_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, env)
+            self.ff_norm = NORMS.build(layer.feed_forward_norm, env)
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError(f"layer {layer.name}: {type(norm).__name__} cannot add the norm of an output to the stream")
+
+    def sub_parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
+
+    def tensor_specs(self):
+        specs = []
+        for part in self.sub_parts():
+            specs += part.tensor_specs()
+        return specs
+
+    def bind(self, tensors):
+        for part in self.sub_parts():
+            part.bind(tensors)
+
+    def mixer_part(self):
+        return self.mixer
+
+    @staticmethod
+    def _rows(y):
+        return y.materialize() if hasattr(y, "materialize") else y
+
+    def forward(self, stream, step, cache):
+        x = stream.rows(self.env)
+        y = self._rows(self.mixer.forward(x, step, cache))
+        stream.current = self.mixer_norm.add_normed(stream.residual, y)
+        if self.feed_forward is not None:
+            y = self._rows(self.feed_forward.forward(stream.rows(self.env), step))
+            stream.current = self.ff_norm.add_normed(stream.residual, y)
+        if stream.observer is not None:
+            stream.observer(stream)

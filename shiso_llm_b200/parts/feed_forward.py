@@ -7,7 +7,8 @@ projection (crates/shiso-engine/src/ffn.rs:234-239); here they are joined into o
 for decode-sized batches and by a kernel of its own otherwise.
 
 ``relu2_ff`` is ``W_down relu(W_up x)^2``; ``routed_experts`` a mixture of gated experts
-behind a router with group-limited choice (see the classes).
+behind a router with group-limited choice; ``polynorm_ff`` is ``W_down act(W_up x)`` with a
+polynomial of unit-RMS powers as the activation (see the classes).
 """
 
 from __future__ import annotations
@@ -15,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..config.errors import UnsupportedShape
-from ..weights.spec import TensorSpec
+from ..weights.spec import NORMAL, VECTOR, TensorSpec
 from .base import FEED_FORWARDS, DeferredLinear, FeedForward, project
 
 MAX_EXPERTS = 256  # what the routing kernel keeps of a token's scores in a warp's registers ...
@@ -79,6 +80,35 @@ class Relu2FeedForward(FeedForward):
     def forward(self, x, step):
         ops = self.env.ops
         mid = ops.unary(project(ops, x, self.up, self.env.dtype), "relu2", self.env.dtype)
+        return DeferredLinear(ops, mid, self.down, self.env.dtype)
+
+
+@FEED_FORWARDS.register("polynorm_ff")
+class PolyNormFeedForward(FeedForward):
+    """``W_down act(W_up x)`` with ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e``: powers element by
+    element, ``N(u) = u / sqrt(mean(u^2) + eps)`` over a token's ``intermediate_size`` values,
+    statistics in float32.  Names ``up``, ``down`` and ``act`` (the four numbers a, b, c, e)."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.eps = float(p["eps"])
+        self.names = (p["up"], p["down"], p["act"])
+        self.up = self.down = self.coefficients = None
+
+    def tensor_specs(self):
+        up, down, act = self.names
+        return [TensorSpec(up, (self.inter, self.hidden)), TensorSpec(down, (self.hidden, self.inter)),
+                TensorSpec(act, (4,), VECTOR, NORMAL, init_mean=0.4, init_std=0.3)]
+
+    def bind(self, tensors):
+        self.up, self.down, self.coefficients = (tensors[n] for n in self.names)
+
+    def forward(self, x, step):
+        ops = self.env.ops
+        mid = ops.polynorm(project(ops, x, self.up, self.env.dtype), self.coefficients, self.eps, self.env.dtype)
         return DeferredLinear(ops, mid, self.down, self.env.dtype)
 
 

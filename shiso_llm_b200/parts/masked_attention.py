@@ -1,0 +1,160 @@
+"""Grouped-query attention whose mask, weighting and head preparation are parameters.
+
+``q = W_q h (+ b_q)`` in ``heads`` of ``dim``, ``k = W_k h (+ b_k)`` in ``kv_heads`` of ``dim``,
+``v = W_v h (+ b_v)`` in ``kv_heads`` of ``vdim``; query head ``a`` reads KV head
+``a // (heads / kv_heads)``.  Then, per query and key head:
+
+  * ``head_norm``: none, or an RMS norm over ``dim`` taken ``"before"`` or ``"after"`` the
+    rotation, with one ``[dim]`` weight for the queries and one for the keys (shared by the
+    heads) or, without names for them, no weight at all (a unit norm);
+  * the position encoding on the first ``rotary_dim`` entries (half-split pairs; cosine and sine
+    times the encoding's ``magnitude``).
+
+``score = (q . k) * scale``, then ``softcap * tanh(score / softcap)`` if a cap is given.  What
+position ``i`` sees (``mask``):
+
+  * ``{"kind": "window", "size": w, "keep_first": f}``: ``j <= i`` with ``i - j < w`` or ``j < f``
+    (the kept first tokens stay at their true positions);
+  * ``{"kind": "chunk", "size": c}``: ``j <= i`` with ``j // c == i // c``, chunks counted from
+    position 0 of the sequence wherever a prompt was cut.
+
+``weights``: ``"softmax"`` over the visible keys, or ``"sigmoid"``: every visible key weighs
+``sigmoid(score + key_bias[head])`` and nothing is normalised.  ``gate`` names a ``[heads,
+hidden]`` matrix: head ``a``'s output is multiplied by ``sigmoid((W_g h)_a)``.  Output: ``W_o``
+on the concatenated heads.
+
+The projections are joined into one matrix ``[q | k | v | gate]`` when bound, so one product
+feeds the kernel that prepares the heads in place and stores keys and values.  The cache keeps
+the last ``size`` positions (a chunk never reaches further back than that) and, for a window
+that keeps first tokens, the pages that hold those.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.errors import UnsupportedShape
+from ..weights.spec import NORMAL, ONES, VECTOR, ZEROS, TensorSpec
+from .base import MIXERS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV
+from .plan import PartSpec
+
+MAX_HEAD_DIM = 256  # what the kernels keep of a head in a warp's registers
+
+
+@MIXERS.register("masked_attention")
+class MaskedAttention(Mixer):
+    """``params``: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``v_head_dim``,
+    ``scale``, ``mask``, ``weights``, optionally ``softcap``, ``head_norm`` (+ ``eps``, ``q_norm``,
+    ``k_norm``), ``position``, ``key_bias``, ``gate``, ``q_bias`` / ``k_bias`` / ``v_bias``, and the
+    names ``q_proj``, ``k_proj``, ``v_proj``, ``out_proj``."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.kv_heads = int(p["num_kv_heads"])
+        self.dim = int(p["head_dim"])
+        self.vdim = int(p.get("v_head_dim") or self.dim)
+        self.scale = float(p["scale"])
+        self.softcap = float(p["softcap"]) if p.get("softcap") is not None else None
+        if self.heads % self.kv_heads:
+            raise UnsupportedShape("num_kv_heads", self.kv_heads, f"does not divide {self.heads} query heads")
+        if not 0 < self.dim <= MAX_HEAD_DIM or not 0 < self.vdim <= MAX_HEAD_DIM:
+            raise UnsupportedShape("head sizes", (self.dim, self.vdim), f"the attention kernels take head sizes up to {MAX_HEAD_DIM}")
+        if self.softcap is not None and self.softcap <= 0.0:
+            raise UnsupportedShape("softcap", self.softcap, "a cap on the scores is positive")
+        mask = p["mask"]
+        self.mask = mask["kind"]
+        self.size = int(mask["size"])
+        self.keep_first = int(mask.get("keep_first") or 0)
+        if self.mask not in ("window", "chunk") or self.size < 1 or self.keep_first < 0:
+            raise UnsupportedShape("mask", dict(mask), "kind 'window' or 'chunk', size at least 1, keep_first not negative")
+        if self.mask == "chunk" and self.keep_first:
+            raise UnsupportedShape("mask", dict(mask), "a chunk keeps no first tokens")
+        self.weights = p.get("weights", "softmax")
+        if self.weights not in ("softmax", "sigmoid"):
+            raise UnsupportedShape("weights", self.weights, "expected 'softmax' or 'sigmoid'")
+        self.head_norm = p.get("head_norm")
+        if self.head_norm not in (None, "before", "after"):
+            raise UnsupportedShape("head_norm", self.head_norm, "expected None, 'before' or 'after'")
+        self.eps = float(p.get("eps", 0.0))
+        self.position = POSITION_ENCODINGS.build(p.get("position") or PartSpec("none"), env, self.dim)
+        if getattr(self.position, "interleaved", False):
+            raise UnsupportedShape("position", p["position"].kind, "the kernel that prepares the heads rotates half-split pairs")
+        self.names = {k: p.get(k) for k in ("q_proj", "k_proj", "v_proj", "out_proj", "q_bias", "k_bias", "v_bias", "q_norm", "k_norm",
+                                             "key_bias", "gate")}
+        if self.names["key_bias"] is not None and self.weights != "sigmoid":
+            raise UnsupportedShape("key_bias", self.names["key_bias"], "a bias per head on the scores changes nothing under a softmax")
+        self.in_matrix = self.in_bias = self.out_matrix = None
+        self.q_weight = self.k_weight = self.key_bias = None
+
+    @property
+    def q_cols(self):
+        return self.heads * self.dim
+
+    @property
+    def kv_cols(self):
+        return self.kv_heads * (self.dim + self.vdim)
+
+    def sub_parts(self):
+        return [self.position]
+
+    def tensor_specs(self):
+        n = self.names
+        specs = [
+            TensorSpec(n["q_proj"], (self.heads * self.dim, self.hidden)),
+            TensorSpec(n["k_proj"], (self.kv_heads * self.dim, self.hidden)),
+            TensorSpec(n["v_proj"], (self.kv_heads * self.vdim, self.hidden)),
+            TensorSpec(n["out_proj"], (self.hidden, self.heads * self.vdim)),
+        ]
+        for key, rows in (("q_bias", self.heads * self.dim), ("k_bias", self.kv_heads * self.dim), ("v_bias", self.kv_heads * self.vdim)):
+            if n[key] is not None:
+                specs.append(TensorSpec(n[key], (rows,), VECTOR, NORMAL))
+        for key in ("q_norm", "k_norm"):
+            if n[key] is not None:
+                specs.append(TensorSpec(n[key], (self.dim,), VECTOR, ONES))
+        if n["key_bias"] is not None:
+            specs.append(TensorSpec(n["key_bias"], (self.heads,), VECTOR, ZEROS))
+        if n["gate"] is not None:
+            specs.append(TensorSpec(n["gate"], (self.heads, self.hidden)))
+        return specs
+
+    def bind(self, tensors):
+        n = self.names
+        mats = [tensors[n[k]] for k in ("q_proj", "k_proj", "v_proj")]
+        if n["gate"] is not None:
+            mats.append(tensors[n["gate"]])
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.in_matrix = torch.cat(mats, dim=0).contiguous()
+        if any(n[k] is not None for k in ("q_bias", "k_bias", "v_bias")):
+            rows = (self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim)
+            parts = [tensors[n[k]].to(torch.float32) if n[k] is not None else torch.zeros(r, dtype=torch.float32, device=self.in_matrix.device)
+                     for k, r in zip(("q_bias", "k_bias", "v_bias"), rows)]
+            if n["gate"] is not None:
+                parts.append(torch.zeros(self.heads, dtype=torch.float32, device=self.in_matrix.device))
+            self.in_bias = torch.cat(parts).contiguous()
+        self.out_matrix = tensors[n["out_proj"]]
+        self.q_weight = tensors[n["q_norm"]] if n["q_norm"] is not None else None
+        self.k_weight = tensors[n["k_norm"]] if n["k_norm"] is not None else None
+        self.key_bias = tensors[n["key_bias"]] if n["key_bias"] is not None else None
+
+    def cache_spec(self):
+        return PagedKV(self.kv_heads, self.dim, self.size, self.vdim, keep_first=self.keep_first)
+
+    def forward(self, x, step, cache):
+        ops = self.env.ops
+        proj = ops.linear(x, self.in_matrix, self.env.dtype, self.in_bias)
+        inv_freq, rotary_dim = self.position.rotary()
+        table = step.block_tables[cache.group]
+        q = ops.head_prepare_store(
+            proj, self.heads, self.kv_heads, self.dim, self.vdim, self.q_weight, self.k_weight, self.eps, self.head_norm,
+            inv_freq, rotary_dim, float(getattr(self.position, "magnitude", 1.0)), step, cache.k, cache.v, table, cache.page_size,
+        )
+        gate = proj[:, self.q_cols + self.kv_cols :] if self.names["gate"] is not None else None
+        out = ops.masked_attention(
+            q, self.heads, cache.k, cache.v, table, cache.page_size, self.scale, self.mask, self.size, self.keep_first, step,
+            sigmoid=self.weights == "sigmoid", key_bias=self.key_bias, softcap=self.softcap, gate=gate,
+        )
+        return DeferredLinear(ops, out, self.out_matrix, self.env.dtype)

@@ -7,7 +7,14 @@ what is normalised.
 
 ``offset`` (default 0) is added to the stored weight once, when it is bound: a checkpoint
 that keeps its norm weights around zero and applies ``1 + w`` asks for ``offset = 1`` and
-every kernel runs unchanged.
+every kernel runs unchanged.  ``scalar`` says that the checkpoint holds ONE number for all
+coordinates (a tensor without dimensions): it is spread over the row when bound.  ``gain``
+(default 1) is a constant multiplied into the weight when bound - a scale on the logits
+rides on the final norm this way.
+
+``add_normed`` is the other way round from ``add_apply``: the norm is taken of a sublayer's
+OUTPUT, and that is added to the residual, ``x <- x + norm(y)``; the sublayers of such a layer
+read the residual itself, so the kernel also hands back the new residual in the compute type.
 """
 
 from __future__ import annotations
@@ -26,17 +33,25 @@ class RMSNorm(Norm):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.offset = float(spec.params.get("offset", 0.0))
+        self.scalar = bool(spec.params.get("scalar", False))
+        self.gain = float(spec.params.get("gain", 1.0))
         self.weight = None
 
     def tensor_specs(self):
+        if self.scalar:
+            return [TensorSpec(self.tensor_name, (), VECTOR, NORMAL if self.offset != 0.0 else ONES, init_std=0.1)]
         if self.offset != 0.0:  # stored around zero
             return [TensorSpec(self.tensor_name, (self.size,), VECTOR, NORMAL, init_std=0.1)]
         return [TensorSpec(self.tensor_name, (self.size,), VECTOR, ONES)]
 
     def bind(self, tensors):
         self.weight = tensors[self.tensor_name]
+        if self.scalar:
+            self.weight = self.weight.to(torch.float32).reshape(1).expand(self.size).contiguous()
         if self.offset != 0.0:
             self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
+        if self.gain != 1.0:
+            self.weight = (self.weight.to(torch.float32) * self.gain).contiguous()
 
     def rms_params(self):
         """``(weight, eps)``: what a kernel that normalises inside a product needs."""
@@ -47,6 +62,11 @@ class RMSNorm(Norm):
 
     def add_apply(self, residual, delta, rows=None):
         return self.env.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, rows)
+
+    def add_normed(self, residual, y, want_rows=True):
+        """``residual += norm(y)`` in float32, in place; returns the new residual rows in the
+        compute type (what the next sublayer reads), or None when they are not wanted."""
+        return self.env.ops.norm_into(residual, y, self.weight, self.eps, want_rows)
 
     def add_apply_linear(self, residual, deferred):
         """``residual += deferred.x @ deferred.w^T`` and the norm of the sum, fused where the

@@ -6,9 +6,21 @@ The inverse frequencies are computed once in float64 and rounded to float32; the
 angle ``pos * inv_freq`` and its sine and cosine are evaluated in float32 inside
 the fused norm + rotate + store kernel (the reference calls ``powf`` per element
 on the device; the ladder is the same).
+
+``rope_stretched`` is the same rotation with the ladder stretched for contexts longer than the
+``original`` one: pair ``i`` of ``n = rotary_dim / 2`` keeps its frequency ``f_i`` where it
+turns often, gets ``f_i / factor`` where it turns rarely, and a blend between.  With
+``d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta)`` - the (fractional) pair that
+turns ``t`` times within ``original`` positions - ``lo = max(floor(d(fast)), 0)``,
+``hi = min(ceil(d(slow)), rotary_dim - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``,
+the frequency is ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``.  Cosine and sine are both
+multiplied by ``magnitude = 0.1 * ln(factor) + 1``; kernels that rotate read it from
+``PositionEncoding.magnitude``.
 """
 
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -29,6 +41,30 @@ class RopeHalfSplit(PositionEncoding):
 
     def rotary(self):
         return self.inv_freq, self.rotary_dim
+
+
+@POSITION_ENCODINGS.register("rope_stretched")
+class RopeStretched(RopeHalfSplit):
+    """``params``: ``theta``, ``rotary_dim``, ``factor``, ``original``, ``fast``, ``slow``."""
+
+    def __init__(self, spec, env, head_dim: int):
+        super().__init__(spec, env, head_dim)
+        p = spec.params
+        factor, original = float(p["factor"]), float(p["original"])
+        fast, slow = float(p["fast"]), float(p["slow"])
+        if factor < 1.0 or original <= 0 or fast <= 0 or slow <= 0 or self.theta <= 1.0:
+            raise UnsupportedShape("rotation stretch", (factor, original, fast, slow), "factor >= 1, positive lengths and turns, theta > 1")
+
+        def pair_turning(times: float) -> float:
+            return self.rotary_dim * math.log(original / (2.0 * math.pi * times)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(pair_turning(fast)), 0)
+        hi = min(math.ceil(pair_turning(slow)), self.rotary_dim - 1)
+        i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+        ladder = self.theta ** (-2.0 * i / self.rotary_dim)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        self.inv_freq = (ladder / factor * ramp + ladder * (1.0 - ramp)).to(torch.float32).to(env.device)
+        self.magnitude = 0.1 * math.log(factor) + 1.0
 
 
 @POSITION_ENCODINGS.register("none")

@@ -321,6 +321,8 @@ def unary(x, kind, out_dtype):
         return (x64 / (1.0 + torch.exp(-x64))).to(out_dtype)
     if kind == "relu2":
         return (torch.relu(x64) ** 2).to(out_dtype)
+    if kind == "copy":
+        return x64.to(out_dtype)
     raise ValueError(kind)
 
 
@@ -534,12 +536,12 @@ def group_rmsnorm(x, weight, eps, groups, out_dtype, gate=None, gate_mode=None):
 # --------------------------------------------------------------------------- latent attention
 
 
-def _rotate_rows(v, positions, inv_freq, rotary_dim):
+def _rotate_rows(v, positions, inv_freq, rotary_dim, magnitude=1.0):
     if not rotary_dim:
         return v
     half = rotary_dim // 2
     angle = positions.to(F64)[:, None] * inv_freq.to(F64)[None, :]
-    cos, sin = torch.cos(angle), torch.sin(angle)
+    cos, sin = torch.cos(angle) * magnitude, torch.sin(angle) * magnitude
     while cos.dim() < v.dim():
         cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
     out = v.clone()
@@ -627,3 +629,90 @@ def routed_experts(x, ids, weights, gate_up, down, extra=None):
             mid = (g * _sigmoid(g) * u)
             out[t] += float(weights[t, j]) * (down[e].to(F64) @ mid)
     return out.to(x.dtype)
+
+
+# --------------------------------------------------------------------------- attention with a parameterised mask and weighting
+
+
+def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_order, inv_freq, rotary_dim, magnitude, step,
+                       k_cache, v_cache, block_table, page_size, store=True):
+    T = proj.shape[0]
+    x = proj.to(F64)
+    q_cols, k_cols = heads * dim, kv_heads * dim
+
+    def norm(v, w):
+        v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        return v if w is None else v * w.to(F64)
+
+    def prepare(v, w):
+        if norm_order == "before":
+            v = norm(v, w)
+        if rotary_dim:
+            v = _rotate_rows(v, step.positions, inv_freq, rotary_dim, magnitude)
+        if norm_order == "after":
+            v = norm(v, w)
+        return v
+
+    q = prepare(x[:, :q_cols].reshape(T, heads, dim), q_w)
+    proj[:, :q_cols] = q.reshape(T, q_cols).to(proj.dtype)
+    if store:
+        k = prepare(x[:, q_cols : q_cols + k_cols].reshape(T, kv_heads, dim), k_w)
+        v = proj[:, q_cols + k_cols : q_cols + k_cols + kv_heads * vdim].reshape(T, kv_heads, vdim)
+        rows = _cache_rows(block_table, step.seq_of_token, step.positions, page_size)
+        k_cache.view(-1, kv_heads, dim)[rows] = k.to(k_cache.dtype)
+        v_cache.view(-1, kv_heads, vdim)[rows] = v.to(v_cache.dtype)
+    return proj[:, :q_cols]
+
+
+def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
+                     key_bias=None, softcap=None, gate=None):
+    T = q.shape[0]
+    kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    q64 = q.to(F64).reshape(T, heads, dim)
+    kf, vf = k_cache.view(-1, kv_heads, dim), v_cache.view(-1, kv_heads, vdim)
+    out = torch.zeros(T, heads, vdim, dtype=F64)
+    seq, pos = step.seq_of_token.tolist(), step.positions.tolist()
+    for t in range(T):
+        i = pos[t]
+        if mask == "chunk":
+            seen = list(range(i // size * size, i + 1))
+        else:
+            first = max(0, i - size + 1)
+            seen = list(range(min(keep_first, first))) + list(range(first, i + 1))
+        ps = torch.tensor(seen)
+        pages = block_table[seq[t]].long()[ps // page_size]
+        assert (pages >= 0).all(), f"row {t} at position {i} reads a page that went back"
+        rows = pages * page_size + ps % page_size
+        k, v = kf[rows].to(F64), vf[rows].to(F64)
+        for h in range(heads):
+            g = h // (heads // kv_heads)
+            s = (k[:, g, :] @ q64[t, h]) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            if sigmoid:
+                w = torch.sigmoid(s + (float(key_bias[h]) if key_bias is not None else 0.0))
+            else:
+                w = torch.softmax(s, dim=0)
+            out[t, h] = w @ v[:, g, :]
+            if gate is not None:
+                out[t, h] *= torch.sigmoid(gate[t, h].to(F64))
+    return out.reshape(T, heads * vdim).to(q.dtype)
+
+
+def norm_into(residual, y, w, eps, want_rows=True):
+    y64 = y.to(F64)
+    total = residual.to(F64) + y64 / torch.sqrt((y64 * y64).mean(-1, keepdim=True) + eps) * w.to(F64)
+    residual.copy_(total.to(residual.dtype))
+    if not want_rows:
+        return None
+    return residual if y.dtype == torch.float32 else residual.to(y.dtype)
+
+
+def polynorm(z, coefficients, eps, out_dtype):
+    z64 = z.to(F64)
+    a, b, c, e = (float(v) for v in coefficients)
+
+    def unit(u):
+        return u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+
+    return (a * unit(z64) + b * unit(z64 * z64) + c * unit(z64 ** 3) + e).to(out_dtype)
