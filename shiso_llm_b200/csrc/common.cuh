@@ -14,6 +14,9 @@
 #include <stdlib.h>
 
 #define SHISO_API extern "C" __attribute__((visibility("default")))
+// C++ functions that kernel files call across files: they live in the base library, which
+// every other kernel library is linked against.
+#define SHISO_SHARED __attribute__((visibility("default")))
 
 // Element type codes passed across the C boundary.
 enum { SHISO_F32 = 0, SHISO_BF16 = 1 };
@@ -92,12 +95,12 @@ __device__ __forceinline__ void pdl_begin() {
     pdl_wait();
 }
 
-bool shiso_pdl_enabled();  // defined in elementwise.cu
+SHISO_SHARED bool shiso_pdl_enabled();  // defined in elementwise.cu
 
 // The word in device memory that a kernel sets when one of its bounded waits ran out
 // (defined in gemm_tcgen05.cu).  The token-picking kernels hand it to the host with their
 // picks: they read it and set it back to zero.
-int* shiso_tc_status_word();
+SHISO_SHARED int* shiso_tc_status_word();
 
 template <typename... KArgs, typename... Args>
 static inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -412,10 +412,12 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const PairParams& p, in
     static int resident_pairs = 0;
     if (resident_pairs == 0) {
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters < 1) {
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+        if (e != cudaSuccess) {
             cudaGetLastError();
-            return SHISO_ERR_UNSUPPORTED;
+            return (int)e;  // the runtime's own reason
         }
+        if (clusters < 1) return SHISO_ERR_UNSUPPORTED;
         resident_pairs = clusters < sm_count / 2 ? clusters : sm_count / 2;
     }
     cfg.gridDim = dim3(2 * (tiles < resident_pairs ? tiles : resident_pairs));

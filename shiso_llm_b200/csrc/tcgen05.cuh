@@ -293,4 +293,4 @@ inline bool tensor_map_paged(const void* ptr, long long rows, int heads, int box
 }  // namespace tc
 
 // The device word a kernel sets when one of its bounded waits ran out (one per process).
-int* shiso_tc_status_word();
+__attribute__((visibility("default"))) int* shiso_tc_status_word();

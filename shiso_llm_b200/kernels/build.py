@@ -1,10 +1,14 @@
-"""Builds the CUDA kernels into one shared library, in the tree, on first use.
+"""Builds the CUDA kernels into shared libraries, in the tree, each on its first use.
 
 Every ``*.cu`` under ``csrc/`` is compiled with nvcc for sm_100a only
-(``-gencode arch=compute_100a,code=sm_100a``) and linked into ``libshiso_b200.so``.
+(``-gencode arch=compute_100a,code=sm_100a``).  The files that the others lean on (the launch
+attribute switch and the status word of bounded waits) form ``libshiso_base.so``; every other
+file becomes a library of its own, ``libshiso_<file>.so``, linked against the base and built
+the first time one of its entry points is called.  A model therefore compiles the kernels it
+runs and no others: a design without recurrences never waits for the recurrence kernels.
 The sources include no PyTorch headers: they export plain C launchers that take device
-pointers and a stream, which Python calls through ctypes.  A hash of the sources and
-flags is stored beside the library; a library whose hash does not match is rebuilt.
+pointers and a stream, which Python calls through ctypes.  A hash of a file's source, the
+headers and the flags is stored beside its object and its library; what does not match is rebuilt.
 The build directory is ``csrc/_build`` when that is writable, else a per-user folder
 under the system's temporary directory, so a read-only checkout or another user still
 works.  A line is printed when compilation starts, per file, and at the end.
@@ -22,7 +26,8 @@ import tempfile
 import time
 
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
-LIB_NAME = "libshiso_b200.so"
+BASE = "base"
+BASE_SOURCES = ("elementwise.cu", "gemm_tcgen05.cu")  # define what every other file calls across files
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
@@ -55,16 +60,6 @@ def _headers() -> list[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
 
 
-def source_hash() -> str:
-    h = hashlib.sha256()
-    for path in sources() + _headers():
-        h.update(os.path.basename(path).encode())
-        with open(path, "rb") as f:
-            h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
-    return h.hexdigest()[:20]
-
-
 def _writable_dir(path: str) -> bool:
     try:
         os.makedirs(path, exist_ok=True)
@@ -92,21 +87,60 @@ def build_dir() -> str:
     raise BuildError(f"neither {in_tree} nor {fallback} is writable: nowhere to build the CUDA kernels")
 
 
-def library_path(create: bool = True) -> str:
-    """Path of an up-to-date library, building it first if needed."""
-    want = source_hash()
-    # An up-to-date library in the tree wins even when the tree is read-only.
-    for d in (os.path.join(CSRC, "_build"),):
-        lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "source_hash")
-        if os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == want:
-            return lib
-    d = build_dir()
-    lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "source_hash")
-    if os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == want:
+def module_of(source: str) -> str:
+    """The library a source file goes into: the base, or one named after the file."""
+    name = os.path.basename(source)
+    return BASE if name in BASE_SOURCES else name[:-3]
+
+
+def modules() -> list[str]:
+    """Every library, the base first."""
+    return [BASE] + sorted({module_of(s) for s in sources()} - {BASE})
+
+
+def _module_sources(module: str) -> list[str]:
+    if module == BASE:
+        return [os.path.join(CSRC, f) for f in BASE_SOURCES]
+    path = os.path.join(CSRC, module + ".cu")
+    if not os.path.isfile(path):
+        raise BuildError(f"no kernel file {module}.cu under {CSRC}")
+    return [path]
+
+
+def lib_name(module: str) -> str:
+    return f"libshiso_{module}.so"
+
+
+def _module_hash(module: str) -> str:
+    h = hashlib.sha256()
+    h.update(LINK_RULE.encode())
+    for src in _module_sources(module):
+        h.update(_object_hash(src).encode())
+    if module != BASE:
+        h.update(_module_hash(BASE).encode())
+    return h.hexdigest()[:20]
+
+
+def _fresh(directory: str, module: str) -> str | None:
+    lib, stamp = os.path.join(directory, lib_name(module)), os.path.join(directory, lib_name(module) + ".hash")
+    if os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == _module_hash(module):
         return lib
+    return None
+
+
+def library_path(module: str = BASE, create: bool = True) -> str:
+    """Path of an up-to-date library of one module, building it (and the base) first if needed."""
+    # An up-to-date library in the tree wins even when the tree is read-only.
+    found = _fresh(os.path.join(CSRC, "_build"), module)
+    if found:
+        return found
+    d = build_dir()
+    found = _fresh(d, module)
+    if found:
+        return found
     if not create:
-        raise BuildError("the CUDA kernel library is not built")
-    return build(d)
+        raise BuildError(f"the CUDA kernel library of {module} is not built")
+    return build([module], d)[module]
 
 
 def _object_hash(src: str) -> str:
@@ -118,6 +152,9 @@ def _object_hash(src: str) -> str:
             h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()[:20]
+
+
+LINK_RULE = "2"  # part of every library's hash: raised when the link line changes
 
 
 def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> str:
@@ -138,33 +175,78 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> str:
     return proc.stderr
 
 
-def build(directory: str | None = None, verbose: bool = False) -> str:
+def _link(nvcc: str, directory: str, module: str, base_lib: str | None) -> str:
+    objs = [os.path.join(directory, os.path.basename(s)[:-3] + ".o") for s in _module_sources(module)]
+    name = lib_name(module)
+    tmp_lib = os.path.join(directory, f".{name}.{os.getpid()}")
+    link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+            "-Xlinker", f"-soname={name}", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", "-Bsymbolic"]
+    if base_lib is not None:
+        # recorded by its soname; the loader has it in the process before any other library.  -Bsymbolic:
+        # a library's calls to functions it defines itself (inline functions with static state
+        # among them) stay inside it whatever else the process has loaded.
+        link.append(base_lib)
+    proc = subprocess.run(link, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"linking {name} failed:\n{proc.stdout}\n{proc.stderr}")
+    lib = os.path.join(directory, name)
+    os.replace(tmp_lib, lib)
+    with open(lib + ".hash", "w") as f:
+        f.write(_module_hash(module) + "\n")
+    return lib
+
+
+def build(wanted: list[str] | None = None, directory: str | None = None, verbose: bool = False) -> dict:
+    """Builds the libraries of ``wanted`` modules (None: all of them) and the base; returns
+    module -> path."""
     nvcc = find_nvcc()
     d = directory or build_dir()
-    srcs = sources()
-    if not srcs:
-        raise BuildError(f"no .cu sources under {CSRC}")
+    wanted = modules() if wanted is None else list(dict.fromkeys([BASE] + list(wanted)))
+    out, todo = {}, []
+    for module in wanted:
+        found = None if verbose else (_fresh(os.path.join(CSRC, "_build"), module) or _fresh(d, module))
+        if found:
+            out[module] = found
+        else:
+            todo.append(module)
+    if not todo:
+        return out
+    srcs = [s for module in todo for s in _module_sources(module)]
     started = time.time()
-    _say(f"compiling {len(srcs)} CUDA files for sm_100a into {d} (first use; this takes a minute or two)")
+    _say(f"compiling {len(srcs)} CUDA file(s) for sm_100a into {d}: {', '.join(os.path.basename(s) for s in srcs)} (first use)")
     objs = [os.path.join(d, os.path.basename(s)[:-3] + ".o") for s in srcs]
     log = []
-    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(os.cpu_count() or 4, 16, len(srcs))) as pool:
         futures = {pool.submit(_compile_one, nvcc, s, o, verbose): s for s, o in zip(srcs, objs)}
         for fut in concurrent.futures.as_completed(futures):
             log.append(fut.result())
-            if log[-1] is not None:
-                _say(f"  compiled {os.path.basename(futures[fut])} ({time.time() - started:.0f} s)")
-    tmp_lib = os.path.join(d, f".{LIB_NAME}.{os.getpid()}")
-    link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
-    proc = subprocess.run(link, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
-    lib = os.path.join(d, LIB_NAME)
-    os.replace(tmp_lib, lib)
-    with open(os.path.join(d, "source_hash"), "w") as f:
-        f.write(source_hash() + "\n")
+            _say(f"  compiled {os.path.basename(futures[fut])} ({time.time() - started:.0f} s)")
+    if BASE in todo:
+        out[BASE] = _link(nvcc, d, BASE, None)
+    for module in todo:
+        if module != BASE:
+            out[module] = _link(nvcc, d, module, out[BASE])
     if verbose:
-        with open(os.path.join(d, "ptxas.log"), "w") as f:
+        with open(os.path.join(d, "ptxas.log"), "a") as f:
             f.write("\n".join(log))
-    _say(f"built {lib} in {time.time() - started:.0f} s")
-    return lib
+    _say(f"built {', '.join(lib_name(m) for m in todo)} in {time.time() - started:.0f} s")
+    return out
+
+
+_EXPORT = None
+
+
+def exports() -> dict:
+    """Entry point -> module, read off the sources (every launcher is marked ``SHISO_API``)."""
+    global _EXPORT
+    if _EXPORT is None:
+        import re
+
+        pattern = re.compile(r"SHISO_API\s+[\w\s\*]*?\b(shiso_\w+)\s*\(")
+        found = {}
+        for src in sources():
+            with open(src, "r", encoding="utf-8") as f:
+                for name in pattern.findall(f.read()):
+                    found[name] = module_of(src)
+        _EXPORT = found
+    return _EXPORT

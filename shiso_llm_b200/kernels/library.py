@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
-from .build import BuildError, library_path
+from .build import BASE, BuildError, exports, library_path
 
 _LIB = None
 
@@ -92,33 +92,63 @@ class KernelLibraryError(RuntimeError):
     pass
 
 
-def library():
-    global _LIB
-    if _LIB is not None:
-        return _LIB
-    try:
-        path = library_path()
-    except BuildError as e:
-        raise KernelLibraryError(f"the CUDA kernels are required and could not be built: {e}") from e
-    try:
-        lib = ctypes.CDLL(path)
-    except OSError as e:
-        raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from e
-    for name, argtypes in _SIGNATURES.items():
+class _Library:
+    """The kernel libraries as one object: an entry point is looked up, on its first use, in the
+    library of the file that defines it, which is built then if it is not yet."""
+
+    def __init__(self):
+        self._loaded = {}
+
+    def _module(self, module: str):
+        lib = self._loaded.get(module)
+        if lib is not None:
+            return lib
+        if module != BASE:
+            self._module(BASE)  # the others resolve their cross-file calls against it
+        try:
+            path = library_path(module)
+        except BuildError as e:
+            raise KernelLibraryError(f"the CUDA kernels are required and could not be built: {e}") from e
+        try:
+            # (never with RTLD_GLOBAL: every library carries its own copies of inline functions and
+            # their static state, and a global base would lend the others its copies)
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from e
+        self._loaded[module] = lib
+        return lib
+
+    def __getattr__(self, name):
+        if not name.startswith("shiso_"):
+            raise AttributeError(name)
+        module = exports().get(name)
+        if module is None:
+            raise KernelLibraryError(f"no kernel file exports {name}")
+        lib = self._module(module)
         try:
             fn = getattr(lib, name)
         except AttributeError as e:
-            raise KernelLibraryError(f"{path} does not export {name}; rebuild it") from e
-        fn.argtypes = argtypes
+            raise KernelLibraryError(f"{lib._name} does not export {name}; rebuild it") from e
+        if name in _SIGNATURES:
+            fn.argtypes = _SIGNATURES[name]
         fn.restype = c_int
-    _LIB = lib
-    return lib
+        setattr(self, name, fn)
+        return fn
+
+    def loaded(self) -> list:
+        return sorted(self._loaded)
+
+
+def library():
+    global _LIB
+    if _LIB is None:
+        _LIB = _Library()
+        _LIB._module(BASE)  # no kernels without it: fail here, loudly, not at the first launch
+    return _LIB
 
 
 def declare(name: str, argtypes) -> None:
     """Declares one more entry point (used by kernels added in their own files)."""
     _SIGNATURES[name] = argtypes
-    if _LIB is not None:
-        fn = getattr(_LIB, name)
-        fn.argtypes = argtypes
-        fn.restype = c_int
+    if _LIB is not None and name in _LIB.__dict__:
+        _LIB.__dict__[name].argtypes = argtypes

@@ -31,7 +31,8 @@ ARRAY_FLOATS = 1 << 20
 def load():
     from shiso_llm_b200.kernels.build import library_path
 
-    lib = ctypes.CDLL(library_path())
+    ctypes.CDLL(library_path())  # the base first: the others are linked against it
+    lib = ctypes.CDLL(library_path("attention_decode"))
     P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.shiso_decode_attention_no_alloc.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P]
     lib.shiso_decode_attention_no_alloc.restype = I
