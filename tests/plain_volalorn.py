@@ -154,4 +154,4 @@ def forward(doc, tensors, tokens, after_layer=None):
         if after_layer is not None:
             after_layer(i, x)
     x = scalar_norm(x, _w(tensors, "final.norm"), eps)
-    return x @ _w(tensors, "head").T * doc["logit_scale"]
+    return x @ _w(tensors, "head").T * doc.get("logit_scale", 1.0)
