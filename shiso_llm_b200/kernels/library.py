@@ -83,6 +83,8 @@ _SIGNATURES = {
     "shiso_latent_prefill": [P, P, P, I, P, P, P, I, I, I, I, I, I, F, P],
     "shiso_head_prepare_store": [P, LL, I, I, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
     "shiso_masked_attention": [P, LL, I, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, F, F, I, I, I, I, P],
+    "shiso_masked_attention_tiles_supported": [I, I],
+    "shiso_masked_attention_tiles": [P, LL, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, I, F, F, I, I, I, I, P],
     "shiso_norm_into": [P, P, I, P, P, I, I, F, P],
     "shiso_polynorm": [P, LL, I, P, P, I, I, F, P],
 }

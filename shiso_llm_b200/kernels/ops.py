@@ -1169,14 +1169,17 @@ def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_ord
 
 
 def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
-                     key_bias=None, softcap=None, gate=None):
+                     key_bias=None, softcap=None, gate=None, general=False):
     """Attention of every row over the keys its mask shows: ``mask`` "window" (the last ``size``
     positions and the first ``keep_first`` of the sequence) or "chunk" (the positions of the row's
     own run of ``size``, counted from 0).  Scores ``(q . k) * scale``, capped as
     ``softcap * tanh(score / softcap)`` when a cap is given; weights a softmax, or with ``sigmoid``
     one ``sigmoid(score + key_bias[head])`` per key, not normalised.  ``gate[T, heads]`` (logits)
     multiplies each head's output by its sigmoid.  ``q`` and ``gate`` may be column ranges.
-    Returns ``[T, heads * vdim]``."""
+    Returns ``[T, heads * vdim]``.  bfloat16 steps that hold prompt portions take the tiled
+    tensor-core kernel (key sizes in multiples of 16 up to 256, value sizes up to 128); steps of
+    single tokens, float32 and other sizes take the general kernel, as does ``general=True``
+    (tests compare the routes)."""
     act = q.dtype
     kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
     q_ld = _rows(q, "q", act, heads * dim)
@@ -1192,13 +1195,32 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
     gate_ld = _rows(gate, "gate", act, heads) if gate is not None else 0
     tokens = q.shape[0]
     out = torch.empty((tokens, heads * vdim), dtype=act, device=q.device)
-    status = library().shiso_masked_attention(
+    lib = library()
+    what = f"({mask}, {'sigmoid' if sigmoid else 'softmax'})"
+    if (
+        not general and act == torch.bfloat16 and not getattr(step, "all_decode", False)
+        and lib.shiso_masked_attention_tiles_supported(dim, vdim)
+    ):
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 64) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 64 + step.num_seqs
+        status = lib.shiso_masked_attention_tiles(
+            q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
+            _ptr(step.start_pos), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
+            step.num_seqs, tiles, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size),
+            int(keep_first), int(bool(sigmoid)), _stream(),
+        )
+        _done(status, f"masked_attention_tiles {what}", shape=(tokens, heads, dim))
+        return out
+    status = lib.shiso_masked_attention(
         q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
         _ptr(step.seq_of_token), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
         tokens, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size), int(keep_first),
         int(bool(sigmoid)), _stream(),
     )
-    _done(status, f"masked_attention ({mask}, {'sigmoid' if sigmoid else 'softmax'})", shape=(tokens, heads, dim))
+    _done(status, f"masked_attention {what}", shape=(tokens, heads, dim))
     return out
 
 

@@ -665,7 +665,7 @@ def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_ord
 
 
 def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
-                     key_bias=None, softcap=None, gate=None):
+                     key_bias=None, softcap=None, gate=None, general=False):
     T = q.shape[0]
     kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
     q64 = q.to(F64).reshape(T, heads, dim)

@@ -1032,3 +1032,42 @@ def test_words_between_pinned_host_memory_and_the_device_by_kernel(words):
         assert ops().words_to_host(on_device, torch.zeros(words - 1, dtype=torch.int32).pin_memory()) is False
         assert ops().words_from_host(torch.zeros(words - 1, dtype=torch.int32).pin_memory(), on_device) is False
     ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("case", [(4, 2, 64, 64, 16), (6, 2, 32, 48, 8), (2, 1, 128, 32, 64), (3, 3, 96, 128, 16), (8, 2, 256, 16, 4),
+                                  (5, 1, 16, 80, 16)])
+def test_masked_attention_tiles(case):
+    """Prompt portions in bfloat16 take the tiled kernel: windows shorter and longer than a tile of
+    keys, with kept first positions inside the first tile, across several, and more of them than
+    the window is wide; chunks whose borders fall inside tiles; capped scores, sigmoid weights
+    with a bias per head, a gate per head; queries and gate as column ranges of wider rows, also
+    rows that no 16 bytes divide.  Against the plain function and against the general kernel."""
+    heads, kv_heads, dim, vdim, page = case
+    q_lens, starts = [5, 1, 130, 64, 2, 65, 200], [0, 37, 3, 70, 333, 0, 190]
+    num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 3
+    cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 170)
+    cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+    dtype = torch.bfloat16
+    k = rnd((num_pages, page, kv_heads, dim), dtype, 171)
+    v = rnd((num_pages, page, kv_heads, vdim), dtype, 172)
+    tokens = sum(q_lens)
+    bias = rnd((heads,), torch.float32, 174)
+    scale = 1.0 / math.sqrt(dim)
+    for extra in (heads, 8 * heads + 3):  # the second makes rows that are no multiple of 16 bytes long
+        rows = rnd((tokens, heads * dim + extra), dtype, 173)
+        q, gate = rows[:, : heads * dim], rows[:, heads * dim : heads * dim + heads]
+        rows_gpu = rows.cuda()
+        q_gpu, gate_gpu = rows_gpu[:, : heads * dim], rows_gpu[:, heads * dim : heads * dim + heads]
+        settings = [("window", 100, 0, False, None, False), ("window", 9, 3, False, None, False), ("window", 70, 130, False, 3.0, True),
+                    ("window", 64, 64, False, None, False), ("chunk", 50, 0, True, 2.5, True), ("chunk", 64, 0, True, None, False),
+                    ("chunk", 7, 0, False, None, True), ("chunk", 1000, 0, True, None, False)]
+        for mask, size, keep, sigmoid, cap, gated in settings:
+            kw = dict(sigmoid=sigmoid, key_bias=bias if sigmoid else None, softcap=cap)
+            want = ref.masked_attention(q, heads, k, v, table, page, scale, mask, size, keep, cpu, gate=gate if gated else None, **kw)
+            kw["key_bias"] = bias.cuda() if sigmoid else None
+            args = (q_gpu, heads, k.cuda(), v.cuda(), table.cuda(), page, scale, mask, size, keep, gpu)
+            got = ops().masked_attention(*args, gate=gate_gpu if gated else None, **kw)
+            what = f"masked attention in tiles {case} {mask} {size} keep {keep} sigmoid {sigmoid} cap {cap} gate {gated}"
+            close(got, want, dtype, what)
+            general = ops().masked_attention(*args, gate=gate_gpu if gated else None, general=True, **kw)
+            close(got, general, dtype, what + " against the general kernel")
