@@ -68,6 +68,8 @@ struct DecodeTmaArgs {
     __nv_bfloat16* out;       // [T, heads * 64]
     int* status;
     int width, heads, kv_heads, page_size, splits, window;
+    int keep_first;           // with a window: the first positions of the sequence stay visible
+    long long q_ld;           // elements between two rows of q
     int cache_rows;           // pages * page size: a row coordinate from here on reads zeros
     float scale_log2;
     // FROM_QKV: the step's rows come straight from the qkv product, [T, (heads + 2 * kv_heads) * 64]
@@ -162,11 +164,16 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const int seq = a.seq_of_token[t];  // asked for beside the position, not after it
     const int lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
     const int first_tile = lo / TILE, last_tile = pos / TILE;
-    const int n_tiles = last_tile - first_tile + 1;
+    // kept first positions that lie before the window's first tile are tiles of their own, ahead of
+    // the others: the parts share out this list, entry v of which is tile tile_at(v)
+    const int keep = a.window > 0 ? a.keep_first : 0;
+    const int kept_tiles = keep > 0 ? min((keep + TILE - 1) / TILE, first_tile) : 0;
+    const int n_tiles = kept_tiles + last_tile - first_tile + 1;
     const int per_part = (n_tiles + a.splits - 1) / a.splits;
     const int parts = (n_tiles + per_part - 1) / per_part;  // parts that have keys
-    const int tile0 = first_tile + split * per_part;
-    const int my_tiles = min(per_part, last_tile + 1 - tile0);
+    const int tile0 = split * per_part;
+    const int my_tiles = min(per_part, n_tiles - tile0);
+    auto tile_at = [&](int v) { return v < kept_tiles ? v : first_tile - kept_tiles + v; };
     if (my_tiles <= 0) {  // uniform: a part past the sequence's end has nothing to send
         if (parts > 1) cluster_meet();
         return;
@@ -202,8 +209,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             const bool on = sub < tiles_per_round && i < my_tiles;
             int row = a.cache_rows;  // a page wholly outside the keys this token sees: zeros
             if (on) {
-                const int key = (tile0 + i) * TILE + pg * a.page_size;
-                if (key <= pos && key + a.page_size > lo) row = table[key / a.page_size] * a.page_size;
+                const int key = tile_at(tile0 + i) * TILE + pg * a.page_size;
+                if (key <= pos && (key + a.page_size > lo || key < keep)) row = table[key / a.page_size] * a.page_size;
             }
             // the cache rows of this step were written by the kernel before - unless this kernel
             // writes them itself: then the caches hold nothing of this step yet, the kernel
@@ -240,7 +247,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         {
             // the group's queries as the 16 rows of the MMA's A operand (rows past the group are zero)
             const int units = a.heads + 2 * a.kv_heads;
-            const __nv_bfloat16* q_rows = FROM_QKV ? a.qkv + (size_t)t * units * HEAD : a.q + (size_t)t * a.heads * HEAD;
+            const __nv_bfloat16* q_rows = FROM_QKV ? a.qkv + (size_t)t * units * HEAD : a.q + (size_t)t * a.q_ld;
             const uint32_t* q_lo = reinterpret_cast<const uint32_t*>(q_rows + (size_t)(g_head * group + min(g, group - 1)) * HEAD);
             const uint32_t* q_hi = reinterpret_cast<const uint32_t*>(q_rows + (size_t)(g_head * group + min(g + 8, group - 1)) * HEAD);
 #pragma unroll
@@ -305,7 +312,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             const uint32_t kt = smem_u32(ring + stage * STAGE_BYTES) + warp * 16 * ROW;
             const uint32_t vt = kt + TILE_BYTES;
-            const int key0 = (tile0 + i) * TILE + warp * 16;
+            const int key0 = tile_at(tile0 + i) * TILE + warp * 16;
             if constexpr (FROM_QKV) {
                 if (a.store && pos >= key0 && pos < key0 + 16) {
                     // This token's own key and value are not in the cache yet: this warp owns their
@@ -357,7 +364,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                         *reinterpret_cast<uint2*>(dst) = lo_raw;
                         *reinterpret_cast<uint2*>(dst + 32) = hi_raw;
                         // the row in the tile: 16-byte piece (l8 >> 1) of the row's low half, piece 4 + .. of its high half
-                        const uint32_t r = (uint32_t)(pos - (tile0 + i) * TILE);
+                        const uint32_t r = (uint32_t)(pos - tile_at(tile0 + i) * TILE);
                         const uint32_t row_addr = smem_u32(ring + stage * STAGE_BYTES) + what * TILE_BYTES + r * ROW;
                         const uint32_t piece = l8 >> 1, inside = (l8 & 1) * 8;
                         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(row_addr + (((piece) ^ (r & 7)) << 4) + inside), "r"(lo_raw.x), "r"(lo_raw.y) : "memory");
@@ -367,7 +374,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     __syncwarp();
                 }
             }
-            if (key0 <= pos && key0 + 16 > lo) {  // warp-uniform: some of this warp's keys are seen
+            if (key0 <= pos && (key0 + 16 > lo || key0 < keep)) {  // warp-uniform: some of this warp's keys are seen
                 float s_acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS; ++kk) {
@@ -384,7 +391,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int key = key0 + j * 8 + t4 * 2 + (e & 1);
-                        const float v = (key >= lo && key <= pos) ? s_acc[j][e] * a.scale_log2 : -INFINITY;
+                        const float v = ((key >= lo || key < keep) && key <= pos) ? s_acc[j][e] * a.scale_log2 : -INFINITY;
                         s_acc[j][e] = v;
                         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
                     }
@@ -605,6 +612,7 @@ int prepare_decode_tma(const void* k_cache, const void* v_cache, const int* bloc
     a->page_size = page_size;
     a->splits = splits;
     a->window = window;
+    a->q_ld = (long long)heads * HEAD;
     a->cache_rows = (int)cache_rows;
     a->scale_log2 = scale * 1.4426950408889634f;
     return SHISO_OK;
@@ -694,5 +702,54 @@ SHISO_API int shiso_decode_attention_from_qkv(const void* qkv, const float* q_w,
     a.v_cache = (__nv_bfloat16*)v_cache;
     a.eps = eps;
     a.store = store;
+    return launch_decode_tma<true>(mk, mv, a, tokens, stream);
+}
+
+// shiso_decode_attention_fused for a window that keeps the first `keep_first` positions of every
+// sequence visible at their true positions; q may be a column range of wider rows (q_ld elements apart).
+SHISO_API int shiso_decode_attention_fused_kept(const void* q, long long q_ld, const void* k_cache, const void* v_cache,
+                                                const int* block_table, int table_width, const int* positions,
+                                                const int* seq_of_token, void* out, int tokens, int heads, int kv_heads,
+                                                int head_dim, int page_size, long long num_pages, float scale, int window,
+                                                int keep_first, int splits, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (((uintptr_t)q & 15) || (q_ld % 8) || keep_first < 0) return SHISO_ERR_ALIGN;
+    DecodeTmaArgs a;
+    CUtensorMap mk, mv;
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token,
+                                          out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
+                                          &mk, &mv);
+    if (status != SHISO_OK) return status;
+    a.q = (const __nv_bfloat16*)q;
+    a.q_ld = q_ld;
+    a.keep_first = keep_first;
+    return launch_decode_tma<false>(mk, mv, a, tokens, stream);
+}
+
+// shiso_decode_attention_from_qkv for a window that keeps the first `keep_first` positions visible.
+SHISO_API int shiso_decode_attention_from_qkv_kept(const void* qkv, const float* q_w, const float* k_w, const float* inv_freq,
+                                                   float eps, void* k_cache, void* v_cache, const int* block_table,
+                                                   int table_width, const int* positions, const int* seq_of_token, void* out,
+                                                   int tokens, int heads, int kv_heads, int head_dim, int page_size,
+                                                   long long num_pages, float scale, int window, int keep_first, int splits,
+                                                   int store, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (!qkv || !q_w || !k_w || !inv_freq || keep_first < 0) return SHISO_ERR_SHAPE;
+    if ((uintptr_t)qkv & 15) return SHISO_ERR_ALIGN;
+    DecodeTmaArgs a;
+    CUtensorMap mk, mv;
+    const int status = prepare_decode_tma(k_cache, v_cache, block_table, table_width, positions, seq_of_token,
+                                          out, tokens, heads, kv_heads, head_dim, page_size, num_pages, scale, window, splits, &a,
+                                          &mk, &mv);
+    if (status != SHISO_OK) return status;
+    a.qkv = (const __nv_bfloat16*)qkv;
+    a.q_w = q_w;
+    a.k_w = k_w;
+    a.inv_freq = inv_freq;
+    a.k_cache = (__nv_bfloat16*)k_cache;
+    a.v_cache = (__nv_bfloat16*)v_cache;
+    a.eps = eps;
+    a.store = store;
+    a.keep_first = keep_first;
     return launch_decode_tma<true>(mk, mv, a, tokens, stream);
 }

@@ -61,6 +61,7 @@ struct TcArgs {
     long long out_ld;
     int* status;
     int width, num_seqs, heads, kv_heads, page_size, window;
+    int keep_first;          // with a window: the first positions of a sequence stay visible to every later row
     int cache_rows;          // pages * page size: a row coordinate from here on reads zeros
     float scale_log2;        // scale * log2(e)
     float out_scale;         // a constant the normalised result is multiplied by
@@ -192,7 +193,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int kv_head = head / (a.heads / a.kv_heads);
     const int key_lo = a.window > 0 ? max(0, first_pos + 1 - a.window) : 0;  // the smallest key any row sees
     const int tile_first = key_lo / BKEY, tile_last = last_pos / BKEY;
-    const int num_tiles = tile_last - tile_first + 1;
+    // kept first positions that lie before the window's first tile come as tiles of their own, ahead of the others
+    const int kept_tiles = a.window > 0 && a.keep_first > 0 ? min((a.keep_first + BKEY - 1) / BKEY, tile_first) : 0;
+    const int num_tiles = kept_tiles + tile_last - tile_first + 1;
+    auto tile_at = [&](int it) { return it < kept_tiles ? it : tile_first - kept_tiles + it; };
     bool failed = false;
 
     pdl_wait();  // queries, keys and values were written by the kernels before this one
@@ -207,9 +211,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int* table = a.block_table + (size_t)seq * a.width;
         const int pages_per_tile = BKEY / a.page_size;
         auto lookup = [&](int it) {
-            const int key = (tile_first + it) * BKEY + lane * a.page_size;
+            const int key = tile_at(it) * BKEY + lane * a.page_size;
             int page = -1;
-            if (lane < pages_per_tile && key <= last_pos && key + a.page_size > key_lo) page = table[key / a.page_size];
+            if (lane < pages_per_tile && key <= last_pos && (key + a.page_size > key_lo || key < a.keep_first)) page = table[key / a.page_size];
             return page >= 0 ? page * a.page_size : a.cache_rows;  // a row past the end of the cache: zeros
         };
         int row_next = lookup(0);
@@ -272,9 +276,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         float row_max = -INFINITY, row_sum = 0.0f;  // the maximum in use (scaled, log2 units) and the sum against it
         for (int it = 0; it < num_tiles; ++it) {
             const int b = it & 1;
-            const int key0 = (tile_first + it) * BKEY;
+            const int key0 = tile_at(it) * BKEY;
             // every key of the tile is seen by every row of the CTA: no mask, nothing to zero
-            const bool open = key0 + BKEY - 1 <= first_pos && (a.window <= 0 || key0 > first_pos + BQ - 1 - a.window);
+            const bool open = it >= kept_tiles && key0 + BKEY - 1 <= first_pos && (a.window <= 0 || key0 > first_pos + BQ - 1 - a.window);
             if (!mbar_wait(&s_full[b], (it >> 1) & 1)) failed = true;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[BKEY];
@@ -288,7 +292,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
                 for (int i = 0; i < BKEY; ++i) {
                     const int key = key0 + i;
-                    if (!(key <= my_pos && (a.window <= 0 || key > my_pos - a.window))) sv[i] = __float_as_uint(-INFINITY);
+                    if (!(key <= my_pos && (a.window <= 0 || key > my_pos - a.window || key < a.keep_first))) sv[i] = __float_as_uint(-INFINITY);
                 }
             }
             float part_max[8];  // eight chains of four links, not one of 64
@@ -349,7 +353,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const int vs = it % STAGES;
                 if (!mbar_wait(&v_full[vs], (it / STAGES) & 1)) failed = true;
                 const int key = key0 + r;
-                if (r < BKEY && (key < key_lo || key > last_pos)) {
+                if (r < BKEY && ((key < key_lo && key >= a.keep_first) || key > last_pos)) {
                     uint4* row = reinterpret_cast<uint4*>(v_s + vs * KV_BYTES + r * ROW);
 #pragma unroll
                     for (int i = 0; i < ROW / 16; ++i) row[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -427,8 +431,9 @@ static bool strided_map(const void* ptr, int rows, int cols, long long ld, CUten
 static int launch_flash_tc(const void* q, long long q_ld, const void* k_cache, const void* v_cache, const int* block_table,
                            int table_width, const int* q_start, const int* start_pos, void* out, long long out_ld,
                            float* log_sum, float out_scale, int tokens, int num_seqs, int max_tiles, int heads, int kv_heads,
-                           int page_size, long long num_pages, float scale, int window, cudaStream_t stream) {
+                           int page_size, long long num_pages, float scale, int window, cudaStream_t stream, int keep_first = 0) {
     if (num_seqs <= 0 || max_tiles <= 0 || tokens <= 0) return SHISO_OK;
+    if (keep_first < 0) return SHISO_ERR_SHAPE;
     if (kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
     if (!shiso_prefill_attention_tc_supported(HEAD, page_size) || max_tiles > 65535) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SHISO_ERR_ALIGN;
@@ -453,6 +458,7 @@ static int launch_flash_tc(const void* q, long long q_ld, const void* k_cache, c
     a.kv_heads = kv_heads;
     a.page_size = page_size;
     a.window = window;
+    a.keep_first = window > 0 ? keep_first : 0;
     a.cache_rows = (int)cache_rows;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.out_scale = out_scale;
@@ -497,4 +503,15 @@ SHISO_API int shiso_prefill_attention_tc_open(const void* q, long long q_ld, con
                                               long long num_pages, float scale, int window, cudaStream_t stream) {
     return launch_flash_tc(q, q_ld, k_cache, v_cache, block_table, table_width, q_start, start_pos, out, out_ld, log_sum, out_scale, tokens,
                            num_seqs, max_tiles, heads, kv_heads, page_size, num_pages, scale, window, stream);
+}
+
+// The same for a window that keeps the first `keep_first` positions of every sequence visible (at
+// their true positions) to all later rows; queries and outputs may be column ranges of wider rows.
+SHISO_API int shiso_prefill_attention_tc_kept(const void* q, long long q_ld, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int table_width, const int* q_start, const int* start_pos,
+                                              void* out, long long out_ld, int tokens, int num_seqs, int max_tiles, int heads,
+                                              int kv_heads, int page_size, long long num_pages, float scale, int window,
+                                              int keep_first, cudaStream_t stream) {
+    return launch_flash_tc(q, q_ld, k_cache, v_cache, block_table, table_width, q_start, start_pos, out, out_ld, nullptr, 1.0f, tokens,
+                           num_seqs, max_tiles, heads, kv_heads, page_size, num_pages, scale, window, stream, keep_first);
 }

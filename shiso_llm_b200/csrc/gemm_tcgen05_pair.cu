@@ -334,6 +334,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
             // four TMEM loads in flight before the one wait (32 gate and 32 up columns for the pair)
             constexpr int ROUND = GLU ? 32 : 64;
+            const bool bias_wide = ((uintptr_t)p.bias & 15) == 0;
 #pragma unroll 1
             for (int c = 0; c < out_per_tile; c += ROUND) {
                 uint32_t r[4][16];
@@ -359,9 +360,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]) * row_scale);
                     } else if (p.bias) {
+                        // read-only loads, four features at once where the vector's address allows it (N is a
+                        // multiple of 8 and `feature` of 16, so four features never straddle the end): they do
+                        // not wait for the stores of the sixteen features before
+                        if (bias_wide) {
+                            const float4* b4 = reinterpret_cast<const float4*>(p.bias + feature);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (feature + i < p.N) v[i] += p.bias[feature + i];
+                            for (int j = 0; j < 4; ++j) {
+                                if (feature + 4 * j < p.N) {
+                                    const float4 b = __ldg(b4 + j);
+                                    v[4 * j] += b.x;
+                                    v[4 * j + 1] += b.y;
+                                    v[4 * j + 2] += b.z;
+                                    v[4 * j + 3] += b.w;
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (feature + i < p.N) v[i] += __ldg(p.bias + feature + i);
+                        }
                     }
                     if (token < p.T && feature < p.N) store16(p, token, feature, v);
                 }

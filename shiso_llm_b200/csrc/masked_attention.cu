@@ -16,9 +16,13 @@
 //
 // The visible keys form two lists in position order - the kept first positions that lie before
 // the window, then the window or chunk - and each list is cut into runs of 32 keys from its
-// start; run c belongs to warp c % 8 and the warps' partial results are merged in warp order.
-// What a row adds up, and in which order, depends on its position only: not on the batch, not
-// on how the sequence was cut into steps, not on the pages.  Scores, weights, statistics and
+// start; run c belongs to warp c % 8 of CTA (c / 8) % splits, the warps' partial results are
+// merged in warp order and, with more than one CTA a (row, head), the CTAs' by a second launch in
+// CTA order (sigmoid weights simply add up; softmax shares are brought to one maximum).  The
+// caller picks `splits` from the mask's size: a row near the end of a window or chunk of 1,024
+// keys is 32 runs, which one CTA walks four deep while most SMs of a decode step idle.
+// What a row adds up, and in which order, depends on its position and on `splits` only: not on
+// how the sequence was cut into steps, not on the pages.  Scores, weights, statistics and
 // output sums are float.
 //
 // Cache rows: row(p) = table[p / page_size] * page_size + p % page_size, as everywhere.
@@ -122,6 +126,108 @@ head_prepare_store_kernel(AT* __restrict__ proj, long long ld, int q_col, int k_
     for (int c = lane; c < vdim; c += 32) vd[c] = vs[c];
 }
 
+// The same for bfloat16 rows whose sizes allow 16-byte accesses (head sizes, the rotation's half
+// and every column offset in multiples of 8): a thread holds 8 neighbouring entries of a head,
+// `group` lanes (a power of two, at least dim / 8) a head, a CTA one row of the step.  The
+// rotation's cosines and sines are formed once per row, in shared memory, not once per head; the
+// partner entries (half a rotation away) come from the lane that holds them.  Which of the two
+// kernels runs depends on the sizes only, so a sequence's cache rows all come from one of them.
+constexpr int MA_VEC_THREADS = 256;
+
+__global__ void __launch_bounds__(MA_VEC_THREADS)
+head_prepare_store_vec_kernel(__nv_bfloat16* __restrict__ proj, long long ld, int q_col, int k_col, int v_col,
+                              const float* __restrict__ q_w, const float* __restrict__ k_w, const float* __restrict__ inv_freq,
+                              const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ table,
+                              int table_width, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int heads,
+                              int kv_heads, int dim, int vdim, int rotary_dim, int page_size, float eps, float magnitude,
+                              int norm_mode, int store, int group) {
+    __shared__ float cs[MA_MAX_DIM / 2], sn[MA_MAX_DIM / 2];
+    pdl_begin();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    for (int i = threadIdx.x; i < half; i += MA_VEC_THREADS) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sn[i] = s * magnitude;
+        cs[i] = c * magnitude;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int sub = threadIdx.x % group, c0 = sub * 8;
+    const int units = heads + (store ? kv_heads : 0);
+    const int per_pass = MA_VEC_THREADS / group * gridDim.y;
+    size_t cache_row = 0;
+    bool have_row = false;
+    if (store) {
+        const int page = table[(size_t)seq_of_token[t] * table_width + pos / page_size];
+        have_row = page >= 0;
+        cache_row = (size_t)max(page, 0) * page_size + pos % page_size;
+    }
+    for (int base = blockIdx.y * (MA_VEC_THREADS / group); base < units; base += per_pass) {  // uniform: every lane takes part in the shuffles
+        const int unit = base + threadIdx.x / group;
+        const bool live = unit < units && c0 < dim;
+        const bool is_q = unit < heads;
+        const int head = is_q ? unit : unit - heads;
+        __nv_bfloat16* src = proj + (size_t)t * ld + (is_q ? q_col : k_col) + (size_t)head * dim + c0;
+        const float* w = is_q ? q_w : k_w;
+        float x[8];
+        if (live) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src);
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[2 * i] = __uint_as_float(words[i] << 16);
+                x[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = 0.0f;
+        }
+        auto unit_norm = [&]() {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+            for (int off = group >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            const float inv = rsqrtf(ss / (float)dim + eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * (w && live ? w[c0 + i] : 1.0f);
+        };
+        if (norm_mode == MA_NORM_BEFORE) unit_norm();
+        if (rotary_dim > 0) {
+            const bool low = c0 < half, turns = c0 < rotary_dim;
+            const int partner = (lane - sub) + (low ? sub + half / 8 : sub - half / 8);
+            const int pair = low ? c0 : c0 - half;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float other = __shfl_sync(0xffffffffu, x[i], turns ? partner : lane);
+                if (turns) x[i] = low ? x[i] * cs[pair + i] - other * sn[pair + i] : x[i] * cs[pair + i] + other * sn[pair + i];
+            }
+        }
+        if (norm_mode == MA_NORM_AFTER) unit_norm();
+        if (!live) continue;
+        uint4 packed;
+        {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            packed = *reinterpret_cast<uint4*>(h);
+        }
+        if (is_q) {
+            *reinterpret_cast<uint4*>(src) = packed;
+            continue;
+        }
+        if (!have_row) continue;
+        *reinterpret_cast<uint4*>(k_cache + (cache_row * kv_heads + head) * dim + c0) = packed;
+    }
+    if (store && have_row) {  // the values: 16-byte pieces, copied as they are
+        const int pieces = kv_heads * vdim / 8;
+        const uint4* vs = reinterpret_cast<const uint4*>(proj + (size_t)t * ld + v_col);
+        uint4* vd = reinterpret_cast<uint4*>(v_cache + cache_row * kv_heads * vdim);
+        for (int i = blockIdx.y * MA_VEC_THREADS + threadIdx.x; i < pieces; i += MA_VEC_THREADS * gridDim.y) vd[i] = vs[i];
+    }
+}
+
 __device__ __forceinline__ float2 ma_load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
 __device__ __forceinline__ float2 ma_load_pair(const __nv_bfloat16* p) {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
@@ -167,6 +273,8 @@ struct MaskedArgs {
     const float* key_bias;  // [heads], sigmoid weighting only; may be null
     long long q_ld, out_ld, gate_ld;
     int table_width, heads, kv_heads, dim, vdim, page_size, mask_kind, size, keep_first;
+    int splits;      // CTAs that share a (row, head)'s runs of keys; more than one: partial results go to `scratch`
+    float* scratch;  // [rows * heads * splits][vdim + 2]: sums, running maximum, sum of weights
     float scale, softcap;
 };
 
@@ -259,7 +367,8 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
     __shared__ float part_acc[MA_WARPS][MA_MAX_DIM];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x / a.heads, head = blockIdx.x % a.heads;
+    const int item = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
+    const int t = item / a.heads, head = item % a.heads;
     const int kv_head = head / (a.heads / a.kv_heads);
     for (int c = threadIdx.x; c < a.dim; c += blockDim.x) sq[c] = to_f32(q[(size_t)t * a.q_ld + (size_t)head * a.dim + c]);
     __syncthreads();
@@ -274,7 +383,7 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
     float acc[MA_PAIRS][2];
 #pragma unroll
     for (int e = 0; e < MA_PAIRS; ++e) acc[e][0] = acc[e][1] = 0.0f;
-    for (int run = warp; run < runs; run += MA_WARPS) {
+    for (int run = split * MA_WARPS + warp; run < runs; run += MA_WARPS * a.splits) {
         if (run < kept_runs)
             ma_fold<AT, SIGMOID>(a, k_cache, v_cache, pages, 0, kept, run * 32, kv_head, sq, bias, running_max, running_sum, acc, lane,
                                  run_weight[warp], run_row[warp]);
@@ -293,6 +402,30 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
         part_acc[warp][c + 1] = acc[e][1];
     }
     __syncthreads();
+    if (a.splits > 1) {
+        // this CTA's share, merged in warp order; the merge kernel adds the shares up in split order
+        float* part = a.scratch + (size_t)blockIdx.x * (a.vdim + 2);
+        float top = -INFINITY, total = 0.0f;
+        float factor[MA_WARPS];
+#pragma unroll
+        for (int w = 0; w < MA_WARPS; ++w) top = fmaxf(top, part_max[w]);
+#pragma unroll
+        for (int w = 0; w < MA_WARPS; ++w) {
+            factor[w] = SIGMOID ? 1.0f : (part_max[w] == -INFINITY ? 0.0f : expf(part_max[w] - top));
+            total += part_sum[w] * factor[w];
+        }
+        for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < MA_WARPS; ++w) sum += part_acc[w][c] * factor[w];
+            part[c] = sum;
+        }
+        if (threadIdx.x == 0) {
+            part[a.vdim] = top;
+            part[a.vdim + 1] = total;
+        }
+        return;
+    }
     AT* dst = out + (size_t)t * a.out_ld + (size_t)head * a.vdim;
     float gated = 1.0f;
     if (gate) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
@@ -327,11 +460,60 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
     }
 }
 
+// Adds up the shares of a (row, head) in split order; softmax shares are brought to one maximum first.
+template <typename AT, bool SIGMOID>
+__global__ void __launch_bounds__(128)
+masked_attention_merge_kernel(AT* out, const AT* __restrict__ gate, MaskedArgs a) {
+    pdl_begin();
+    const int t = blockIdx.x / a.heads, head = blockIdx.x % a.heads;
+    const float* parts = a.scratch + (size_t)blockIdx.x * a.splits * (a.vdim + 2);
+    AT* dst = out + (size_t)t * a.out_ld + (size_t)head * a.vdim;
+    float gated = 1.0f;
+    if (gate) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
+    float top = -INFINITY, total = 0.0f;
+    if (!SIGMOID) {
+        for (int s = 0; s < a.splits; ++s) top = fmaxf(top, parts[(size_t)s * (a.vdim + 2) + a.vdim]);
+        if (top == -INFINITY) {
+            for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) dst[c] = from_f32<AT>(0.0f);
+            return;
+        }
+        for (int s = 0; s < a.splits; ++s) {
+            const float m = parts[(size_t)s * (a.vdim + 2) + a.vdim];
+            total += parts[(size_t)s * (a.vdim + 2) + a.vdim + 1] * (m == -INFINITY ? 0.0f : expf(m - top));
+        }
+    }
+    for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float* part = parts + (size_t)s * (a.vdim + 2);
+            const float f = SIGMOID ? 1.0f : (part[a.vdim] == -INFINITY ? 0.0f : expf(part[a.vdim] - top));
+            sum += part[c] * f;
+        }
+        dst[c] = from_f32<AT>((SIGMOID ? sum : sum / total) * gated);
+    }
+}
+
 template <typename AT>
 int launch_prepare(void* proj, long long ld, int q_col, int k_col, int v_col, const float* q_w, const float* k_w, const float* inv_freq,
                    const int* positions, const int* seq_of_token, const int* table, int table_width, void* k_cache, void* v_cache,
                    int tokens, int heads, int kv_heads, int dim, int vdim, int rotary_dim, int page_size, float eps, float magnitude,
                    int norm_mode, int store, cudaStream_t stream) {
+    if constexpr (sizeof(AT) == 2) {
+        const bool wide = dim % 8 == 0 && vdim % 8 == 0 && rotary_dim % 16 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 &&
+                          v_col % 8 == 0 && !(((uintptr_t)proj | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
+        if (wide) {
+            int group = 1;
+            while (group * 8 < dim) group *= 2;
+            const int units = heads + (store ? kv_heads : 0);
+            // a row's heads are shared out over CTAs of 256 / group heads
+            const int passes = ceil_div_u(units * group, MA_VEC_THREADS);
+            const dim3 vgrid(tokens, passes);
+            launch_kernel(head_prepare_store_vec_kernel, vgrid, MA_VEC_THREADS, 0, stream, (__nv_bfloat16*)proj, ld, q_col, k_col, v_col, q_w,
+                          k_w, inv_freq, positions, seq_of_token, table, table_width, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads,
+                          kv_heads, dim, vdim, rotary_dim, page_size, eps, magnitude, norm_mode, store, group);
+            return launch_status();
+        }
+    }
     const dim3 grid(tokens, ceil_div_u(heads + (store ? kv_heads : 0), MA_WARPS));
     launch_kernel(head_prepare_store_kernel<AT>, grid, MA_WARPS * 32, 0, stream, (AT*)proj, ld, q_col, k_col, v_col, q_w, k_w, inv_freq,
                   positions, seq_of_token, table, table_width, (AT*)k_cache, (AT*)v_cache, heads, kv_heads, dim, vdim, rotary_dim,
@@ -342,13 +524,21 @@ int launch_prepare(void* proj, long long ld, int q_col, int k_col, int v_col, co
 template <typename AT>
 int launch_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const void* gate, const MaskedArgs& a,
                      int tokens, int sigmoid, cudaStream_t stream) {
-    const unsigned blocks = (unsigned)tokens * a.heads;
+    const unsigned items = (unsigned)tokens * a.heads, blocks = items * a.splits;
     if (sigmoid)
         launch_kernel(masked_attention_kernel<AT, true>, blocks, MA_WARPS * 32, 0, stream, (const AT*)q, (const AT*)k_cache,
                       (const AT*)v_cache, (AT*)out, (const AT*)gate, a);
     else
         launch_kernel(masked_attention_kernel<AT, false>, blocks, MA_WARPS * 32, 0, stream, (const AT*)q, (const AT*)k_cache,
                       (const AT*)v_cache, (AT*)out, (const AT*)gate, a);
+    if (a.splits > 1) {
+        const int first = launch_status();
+        if (first != SHISO_OK) return first;
+        if (sigmoid)
+            launch_kernel(masked_attention_merge_kernel<AT, true>, items, 128, 0, stream, (AT*)out, (const AT*)gate, a);
+        else
+            launch_kernel(masked_attention_merge_kernel<AT, false>, items, 128, 0, stream, (AT*)out, (const AT*)gate, a);
+    }
     return launch_status();
 }
 
@@ -379,12 +569,14 @@ SHISO_API int shiso_masked_attention(const void* q, long long q_ld, int act_dtyp
                                      const int* table, int table_width, const int* positions, const int* seq_of_token, void* out,
                                      long long out_ld, const void* gate, long long gate_ld, const float* key_bias, int tokens,
                                      int heads, int kv_heads, int dim, int vdim, int page_size, float scale, float softcap,
-                                     int mask_kind, int size, int keep_first, int sigmoid, cudaStream_t stream) {
+                                     int mask_kind, int size, int keep_first, int sigmoid, int splits, float* scratch,
+                                     cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
+    if (splits < 1 || (splits > 1 && !scratch)) return SHISO_ERR_SHAPE;
     if (dim <= 0 || dim > MA_MAX_DIM || vdim <= 0 || vdim > MA_MAX_DIM || kv_heads <= 0 || heads % kv_heads || size < 1 || keep_first < 0 ||
         (mask_kind != MA_MASK_WINDOW && mask_kind != MA_MASK_CHUNK))
         return SHISO_ERR_SHAPE;
-    if ((long long)tokens * heads > 0x7fffffffLL) return SHISO_ERR_SHAPE;
+    if ((long long)tokens * heads * splits > 0x7fffffffLL) return SHISO_ERR_SHAPE;
     MaskedArgs a;
     a.table = table;
     a.positions = positions;
@@ -402,6 +594,8 @@ SHISO_API int shiso_masked_attention(const void* q, long long q_ld, int act_dtyp
     a.mask_kind = mask_kind;
     a.size = size;
     a.keep_first = keep_first;
+    a.splits = splits;
+    a.scratch = scratch;
     a.scale = scale;
     a.softcap = softcap;
     if (act_dtype == SHISO_F32) return launch_attention<float>(q, k_cache, v_cache, out, gate, a, tokens, sigmoid, stream);

@@ -68,6 +68,9 @@ _SIGNATURES = {
     "shiso_pool_kv": [P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
     "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, F, I, I, F, P],
     "shiso_prefill_attention_tc_open": [P, LL, P, P, P, I, P, P, P, LL, P, F, I, I, I, I, I, I, LL, F, I, P],
+    "shiso_prefill_attention_tc_kept": [P, LL, P, P, P, I, P, P, P, LL, I, I, I, I, I, I, LL, F, I, I, P],
+    "shiso_decode_attention_from_qkv_kept": [P, P, P, P, F, P, P, P, I, P, P, P, I, I, I, I, I, LL, F, I, I, I, I, P],
+    "shiso_decode_attention_fused_kept": [P, LL, P, P, P, I, P, P, P, I, I, I, I, I, LL, F, I, I, I, P],
     "shiso_add_layernorm": [P, P, P, P, P, P, I, I, I, F, P],
     "shiso_group_rmsnorm": [P, I, LL, P, LL, P, P, I, I, I, I, I, F, P],
     "shiso_causal_conv": [P, LL, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
@@ -82,7 +85,7 @@ _SIGNATURES = {
     "shiso_latent_prefill_supported": [I, I],
     "shiso_latent_prefill": [P, P, P, I, P, P, P, I, I, I, I, I, I, F, P],
     "shiso_head_prepare_store": [P, LL, I, I, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
-    "shiso_masked_attention": [P, LL, I, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, F, F, I, I, I, I, P],
+    "shiso_masked_attention": [P, LL, I, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, F, F, I, I, I, I, I, P, P],
     "shiso_masked_attention_tiles_supported": [I, I],
     "shiso_masked_attention_tiles": [P, LL, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, I, F, F, I, I, I, I, P],
     "shiso_norm_into": [P, P, I, P, P, I, I, F, P],

@@ -695,13 +695,14 @@ DECODE_FROM_QKV_MAX_TOKENS = 64  # rows up to which attention takes the qkv rows
 
 
 def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim, step,
-                              k_cache, v_cache, block_table, page_size, store, scale, window, interleaved=False):
+                              k_cache, v_cache, block_table, page_size, store, scale, window, interleaved=False, keep_first=0):
     """``qk_norm_rope_store`` and ``paged_attention`` in one launch for steps of single tokens:
     the attention kernel takes the rows of the qkv product, norms and rotates the queries and
     each token's new key itself, and (with ``store``) writes the new key and value into the
     caches, with the bits ``qk_norm_rope_store`` would write.  bfloat16, heads of 64 rotated
     whole, both norms present, a handful of rows; None when the step or the sizes are others (the
-    caller then runs the two kernels)."""
+    caller then runs the two kernels).  With a ``window``, the first ``keep_first`` positions of a
+    sequence stay visible."""
     lib = library()
     if (
         qkv.shape[0] > DECODE_FROM_QKV_MAX_TOKENS or qkv.dtype != torch.bfloat16 or not getattr(step, "all_decode", False) or q_w is None or k_w is None
@@ -725,6 +726,17 @@ def decode_attention_from_qkv(qkv, heads, kv_heads, head_dim, q_w, k_w, eps, inv
     if q_w.shape[0] != head_dim or k_w.shape[0] != head_dim or inv_freq.shape[0] != rotary_dim // 2:
         raise KernelError("norm weights of the head size and one frequency per rotated pair are expected")
     out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if keep_first and window:
+        # the keys a row reads are bounded by the window, whatever the table could hold
+        splits = decode_splits(tokens, kv_heads, min(block_table.shape[1] * page_size, int(window) + int(keep_first) + 128), True)
+        status = lib.shiso_decode_attention_from_qkv_kept(
+            _ptr(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), float(eps), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+            block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), _ptr(out),
+            tokens, heads, kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), int(keep_first), splits,
+            int(bool(store)), _stream(),
+        )
+        _done(status, "decode_attention_from_qkv (kept first)", shape=(tokens, heads, head_dim))
+        return out
     splits = decode_splits(tokens, kv_heads, block_table.shape[1] * page_size, True)
     status = lib.shiso_decode_attention_from_qkv(
         _ptr(qkv), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), float(eps), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
@@ -1126,6 +1138,8 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
 _HEAD_NORMS = {None: 0, "before": 1, "after": 2}
 _MASKS = {"window": 0, "chunk": 1}
 MASKED_MAX_HEAD_DIM = 256  # what the kernels of this group keep of a head in a warp's registers
+MASKED_MAX_SPLITS = 16  # CTAs that share a (row, head)'s keys in the general kernel
+MASKED_SCRATCH_BYTES = 64 << 20  # their partial results, at most; larger steps take one CTA a (row, head)
 
 
 def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_order, inv_freq, rotary_dim, magnitude, step,
@@ -1197,6 +1211,42 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
     out = torch.empty((tokens, heads * vdim), dtype=act, device=q.device)
     lib = library()
     what = f"({mask}, {'sigmoid' if sigmoid else 'softmax'})"
+    # A softmax over a window (with or without kept first tokens), heads of 64, no cap and no gate is
+    # what the framework's tensor-memory prompt kernel and its TMA decode kernel compute: they take
+    # the first positions as tiles of their own ahead of the window's.
+    plain_window = (
+        not general and act == torch.bfloat16 and mask == "window" and not sigmoid and not softcap and gate is None
+        and dim == vdim and q.data_ptr() % 16 == 0 and q_ld % 8 == 0
+    )
+    if (
+        plain_window and getattr(step, "all_decode", False) and heads // kv_heads <= MAX_DECODE_GROUP
+        and lib.shiso_decode_attention_fused_supported(heads, kv_heads, dim, page_size)
+    ):
+        splits = decode_splits(tokens, kv_heads, min(block_table.shape[1] * page_size, size + keep_first + 2 * 64), True)
+        status = lib.shiso_decode_attention_fused_kept(
+            q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+            _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, dim, page_size, k_cache.shape[0], float(scale), int(size),
+            int(keep_first), splits, _stream(),
+        )
+        _done(status, f"decode_attention (fused) {what}", shape=(tokens, heads, dim))
+        return out
+    if (
+        plain_window and not getattr(step, "all_decode", False) and tokens >= TC_ATTENTION_MIN_TOKENS
+        and getattr(step, "max_q_len", tokens) >= TC_ATTENTION_MIN_PORTION
+        and lib.shiso_prefill_attention_tc_supported(dim, page_size)
+    ):
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 128) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 128 + step.num_seqs
+        status = lib.shiso_prefill_attention_tc_kept(
+            q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
+            _ptr(step.start_pos), _ptr(out), heads * vdim, tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
+            k_cache.shape[0], float(scale), int(size), int(keep_first), _stream(),
+        )
+        _done(status, f"prefill_attention (tcgen05) {what}", shape=(tokens, heads, dim))
+        return out
     if (
         not general and act == torch.bfloat16 and not getattr(step, "all_decode", False)
         and lib.shiso_masked_attention_tiles_supported(dim, vdim)
@@ -1214,13 +1264,19 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
         )
         _done(status, f"masked_attention_tiles {what}", shape=(tokens, heads, dim))
         return out
+    # CTAs a (row, head): one per 256 keys the mask can show (a number of the layer, not of the
+    # step), while their partial results stay small; a second launch adds them up
+    splits = max(1, min(MASKED_MAX_SPLITS, -(-(int(size) + int(keep_first)) // 256)))
+    if tokens * heads * splits * (vdim + 2) * 4 > MASKED_SCRATCH_BYTES:
+        splits = 1
+    scratch = torch.empty((tokens * heads * splits * (vdim + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
     status = lib.shiso_masked_attention(
         q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
         _ptr(step.seq_of_token), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
         tokens, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size), int(keep_first),
-        int(bool(sigmoid)), _stream(),
+        int(bool(sigmoid)), splits, _ptr(scratch), _stream(),
     )
-    _done(status, f"masked_attention {what}", shape=(tokens, heads, dim))
+    _done(status, f"masked_attention {what}", 2 if splits > 1 else 1, shape=(tokens, heads, dim))
     return out
 
 

@@ -148,6 +148,20 @@ class MaskedAttention(Mixer):
         proj = ops.linear(x, self.in_matrix, self.env.dtype, self.in_bias)
         inv_freq, rotary_dim = self.position.rotary()
         table = step.block_tables[cache.group]
+        from_qkv = getattr(ops, "decode_attention_from_qkv", None)
+        if (
+            from_qkv is not None and self.mask == "window" and self.weights == "softmax" and self.softcap is None
+            and self.names["gate"] is None and self.head_norm == "before" and self.q_weight is not None and self.k_weight is not None
+            and self.dim == self.vdim and float(getattr(self.position, "magnitude", 1.0)) == 1.0
+        ):
+            # steps of single tokens, heads of 64 rotated whole: norm, rotation, cache store and
+            # attention in the one launch the framework's other attention layers take (None otherwise)
+            attn = from_qkv(
+                proj, self.heads, self.kv_heads, self.dim, self.q_weight, self.k_weight, self.eps, inv_freq, rotary_dim, step,
+                cache.k, cache.v, table, cache.page_size, True, self.scale, self.size, keep_first=self.keep_first,
+            )
+            if attn is not None:
+                return DeferredLinear(ops, attn, self.out_matrix, self.env.dtype)
         q = ops.head_prepare_store(
             proj, self.heads, self.kv_heads, self.dim, self.vdim, self.q_weight, self.k_weight, self.eps, self.head_norm,
             inv_freq, rotary_dim, float(getattr(self.position, "magnitude", 1.0)), step, cache.k, cache.v, table, cache.page_size,

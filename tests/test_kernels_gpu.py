@@ -1071,3 +1071,73 @@ def test_masked_attention_tiles(case):
             close(got, want, dtype, what)
             general = ops().masked_attention(*args, gate=gate_gpu if gated else None, general=True, **kw)
             close(got, general, dtype, what + " against the general kernel")
+
+
+@pytest.mark.parametrize("page", [16, 64])
+def test_masked_attention_plain_window_takes_the_framework_kernels(page):
+    """A softmax over a window with kept first positions, heads of 64, no cap and no gate runs on
+    the tensor-memory prompt kernel (long portions) and on the TMA decode kernel (single tokens):
+    first positions inside the window's first tile, tiles before it, more of them than a tile,
+    more than the window; windows that are, and are not, multiples of a tile.  Against the plain
+    function and against the general kernel."""
+    heads, kv_heads, dim = 8, 2, 64
+    dtype = torch.bfloat16
+    scale = 0.11
+    settings = [(100, 0), (64, 5), (200, 70), (130, 130), (64, 64), (1000, 4), (1, 1), (33, 200)]
+    for all_decode, q_lens, starts in (
+        (False, [300, 130, 1, 140, 256], [0, 500, 37, 70, 128]),
+        (True, [1] * 9, [0, 3, 63, 64, 700, 1500, 129, 1100, 191]),
+    ):
+        num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 3
+        cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 180 + page)
+        cpu.h_q_start = gpu.h_q_start = cpu.q_start.tolist()
+        cpu.all_decode = gpu.all_decode = all_decode
+        cpu.max_q_len = gpu.max_q_len = max(q_lens)
+        k = rnd((num_pages, page, kv_heads, dim), dtype, 181)
+        v = rnd((num_pages, page, kv_heads, dim), dtype, 182)
+        tokens = sum(q_lens)
+        rows = rnd((tokens, heads * dim + 16), dtype, 183)  # queries as a column range of wider rows
+        q, q_gpu = rows[:, : heads * dim], rows.cuda()[:, : heads * dim]
+        for size, keep in settings:
+            want = ref.masked_attention(q, heads, k, v, table, page, scale, "window", size, keep, cpu)
+            args = (q_gpu, heads, k.cuda(), v.cuda(), table.cuda(), page, scale, "window", size, keep, gpu)
+            got = ops().masked_attention(*args)
+            what = f"window {size} keep {keep} page {page} decode {all_decode}"
+            close(got, want, dtype, what)
+            general = ops().masked_attention(*args, general=True)
+            close(got, general, dtype, what + " against the general kernel")
+    ops().check_kernel_status()
+
+
+@pytest.mark.parametrize("case", [(8, 2, 64, 64, 64, "before", True), (4, 4, 128, 64, 64, "after", False), (3, 1, 256, 128, 32, None, True),
+                                  (5, 1, 40, 24, 16, "before", False), (2, 2, 64, 64, 0, "after", True)])
+def test_head_prepare_store_wide_rows(case):
+    """Head sizes in multiples of 8 take the kernel that moves 16 bytes a thread: norm before or
+    after the rotation or none, with and without weights, rotations over all or part of a head
+    or none, at few rows and many."""
+    heads, kv_heads, dim, vdim, rot, order, weighted = case
+    page = 16
+    dtype = torch.bfloat16
+    for q_lens, starts in (([1, 1, 1], [5, 700, 64]), ([130, 3, 70], [0, 37, 1000])):
+        num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, q_lens)) + 2
+        cpu, gpu, table = make_step(q_lens, starts, page, num_pages, 190)
+        tokens = sum(q_lens)
+        cols = (heads + kv_heads) * dim + kv_heads * vdim
+        proj = rnd((tokens, cols + 8), dtype, 191)
+        q_w = (1.0 + 0.2 * rnd((dim,), torch.float32, 192)) if weighted else None
+        k_w = (1.0 + 0.2 * rnd((dim,), torch.float32, 193)) if weighted else None
+        inv_freq = (10000.0 ** (-torch.arange(rot // 2, dtype=torch.float32) * 2 / max(rot, 1))) if rot else None
+        k = torch.zeros((num_pages, page, kv_heads, dim), dtype=dtype)
+        v = torch.zeros((num_pages, page, kv_heads, vdim), dtype=dtype)
+        want_rows = proj.clone()
+        want_k, want_v = k.clone(), v.clone()
+        ref.head_prepare_store(want_rows, heads, kv_heads, dim, vdim, q_w, k_w, 1e-5, order, inv_freq, rot, 1.3, cpu, want_k, want_v, table, page)
+        got_rows, got_k, got_v = proj.cuda(), k.cuda(), v.cuda()
+        ops().head_prepare_store(got_rows, heads, kv_heads, dim, vdim, q_w.cuda() if weighted else None, k_w.cuda() if weighted else None,
+                                 1e-5, order, inv_freq.cuda() if rot else None, rot, 1.3, gpu, got_k, got_v, table.cuda(), page)
+        what = f"head preparation {case} rows {tokens}"
+        # the angle position x frequency is a float: its rounding at position 1,000 moves a rotated value by 1e-4 of the largest
+        close(got_rows, want_rows, dtype, what + " (queries)", slack=2e-4)
+        close(got_k, want_k, dtype, what + " (keys)", slack=2e-4)
+        assert torch.equal(got_v.cpu(), want_v), what + " (values)"
+    ops().check_kernel_status()

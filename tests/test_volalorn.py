@@ -267,6 +267,8 @@ DOC_WIDE = {
         layer("attention", chunked(6, 2, 32, 48, 256, 32, 1000.0, 0.18, 15.0, (8.0, 128, 16.0, 1.0)), 96),
         layer("attention_2", windowed(2, 1, 128, 32, 77, 130, 64, 5000.0, 0.09), None),
         layer("attention", chunked(2, 2, 96, 128, 100, 48, 300.0, 0.1), 64),
+        # heads of 64 rotated whole: single tokens take norm, rotation, store and attention in one launch
+        layer("attention_2", windowed(4, 1, 64, 64, 130, 70, 64, 10000.0, 0.125), 96),
     ],
 }
 
