@@ -250,7 +250,7 @@ __device__ __forceinline__ float ma_dot(const float* __restrict__ q, const float
 __device__ __forceinline__ float ma_dot(const float* __restrict__ q, const __nv_bfloat16* __restrict__ key, int dim, bool wide) {
     float dot = 0.0f;
     if (wide) {
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < dim; c += 8) {
             const uint4 raw = *reinterpret_cast<const uint4*>(key + c);
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
