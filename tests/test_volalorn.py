@@ -324,6 +324,33 @@ def test_replay_through_the_trace_runner(tmp_path, dtype):
         check_rows(got, reference_logits(doc, tensors, requests[rid]), dtype, f"{dtype} {trace_id}")
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_of_long_requests_through_the_trace_runner(tmp_path, dtype):
+    """``bin/trace_run`` with heads of real widths and requests of hundreds of tokens: whole (the
+    kernels for long portions), the last 40 tokens one by one (the kernels for single tokens, over
+    windows and chunks that are full), long and short portions, and a mixed trace with portions up
+    to 200 tokens beside single tokens, in a pool that the three requests fill."""
+    doc = DOC_WIDE
+    model_dir = tmp_path / "model"
+    tensors = helpers.make_folder(model_dir, doc, 11, std=0.08)
+    lengths = [700, 150, 300]
+    requests = {f"r{i}": helpers.random_prompt(n, doc["vocab"], 80 + i) for i, n in enumerate(lengths)}
+    steps, expect = [], []
+    for rid, toks in requests.items():
+        steps += helpers.whole(f"w-{rid}", toks)
+        expect.append((f"w-{rid}", rid))
+    steps += helpers.tail_one_by_one("t-r0", requests["r0"], 40)
+    steps += helpers.portions("p-r0", requests["r0"], [300, 100, 258, 2, 1, 39])
+    expect += [("t-r0", "r0"), ("p-r0", "r0")]
+    steps += replay.mixed_trace({f"m-{k}": v for k, v in requests.items()}, 7, 1280, portion_sizes=(2, 5, 64, 130, 200))
+    expect += [(f"m-{rid}", rid) for rid in requests]
+    rows = replay.run_trace_run(model_dir, dtype, steps, 1280, tmp_path / "out", doc["vocab"])
+    for trace_id, rid in expect:
+        got = replay.stack_rows(rows, trace_id, len(requests[rid]))
+        check_rows(got, reference_logits(doc, tensors, requests[rid]), dtype, f"{dtype} {trace_id}")
+
+
 @pytest.mark.parametrize("backend", BACKENDS)
 def test_greedy_generation_through_the_scheduler(tmp_path, backend):
     doc, seed = DOCS["A"]
