@@ -59,6 +59,8 @@ class GqaAttention(Mixer):
         if self.q_norm is not None and self.k_norm is not None and self.q_norm.eps != self.k_norm.eps:
             raise UnsupportedShape("qk norm eps", (self.q_norm.eps, self.k_norm.eps), "q and k norms share one kernel and one eps")
         self.position = POSITION_ENCODINGS.build(p["position"], env, self.head_dim)
+        if float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+            raise UnsupportedShape("position", type(self.position).__name__, "this mixer's kernels rotate without a magnitude on cosine and sine")
         self.qkv = None
         self.out = None
 

@@ -57,6 +57,8 @@ class LatentAttention(Mixer):
         if self.kv_rank > MAX_LATENT_RANK:
             raise UnsupportedShape("kv_rank", self.kv_rank, f"the attention kernel takes latents of up to {MAX_LATENT_RANK}")
         self.position = POSITION_ENCODINGS.build(p["position"], env, self.rot)
+        if float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+            raise UnsupportedShape("position", type(self.position).__name__, "this mixer's kernels rotate without a magnitude on cosine and sine")
         if getattr(self.position, "interleaved", False):
             raise UnsupportedShape("position", p["position"].kind, "the kernels rotate half-split pairs")
         self.names = {k: p[k] for k in ("q_down", "q_norm", "q_up", "kv_down", "kv_norm", "k_up", "v_up", "gate", "out_proj")}

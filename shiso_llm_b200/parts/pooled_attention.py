@@ -58,6 +58,8 @@ class PooledWindowAttention(Mixer):
         if self.window < 1 or self.pool < 1:
             raise UnsupportedShape("window / pool", (self.window, self.pool), "both are at least 1")
         self.position = POSITION_ENCODINGS.build(p.get("position") or PartSpec("none"), env, self.dim)
+        if float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+            raise UnsupportedShape("position", type(self.position).__name__, "this mixer's kernels rotate without a magnitude on cosine and sine")
         if self.position.rotary()[1]:
             raise UnsupportedShape("position", p["position"].kind, "the store kernel of this mixer keeps keys as they are projected")
         self.names = {k: p[k] for k in ("q_proj", "k_proj", "v_proj", "out_proj")}

@@ -53,6 +53,8 @@ class Retention(Mixer):
         # what the kernel multiplies by: S - (1 - decay) S, with 1 - decay formed in float64
         self.losses = (1.0 - torch.tensor(decays, dtype=torch.float64)).to(torch.float32).to(env.device)
         self.position = POSITION_ENCODINGS.build(p["position"], env, self.dim)
+        if float(getattr(self.position, "magnitude", 1.0)) != 1.0:
+            raise UnsupportedShape("position", type(self.position).__name__, "this mixer's kernels rotate without a magnitude on cosine and sine")
         if getattr(self.position, "interleaved", False):
             raise UnsupportedShape("position", p["position"].kind, "the recurrence kernel rotates half-split pairs")
         self.names = {k: p[k] for k in ("q_proj", "k_proj", "v_proj", "g_proj", "out_proj")}
