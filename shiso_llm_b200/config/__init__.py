@@ -15,9 +15,11 @@ from . import lfm2  # registers Lfm2ForCausalLM
 from . import filulix  # registers Filulix
 from . import zetavik  # registers Zetavik
 from . import volalorn  # registers Volalorn
+from . import povilorn  # registers Povilorn
 from .filulix import FilulixConfig
 from .zetavik import ZetavikConfig
 from .volalorn import VolalornConfig
+from .povilorn import PovilornConfig
 from .lfm2 import Lfm2Config, feed_forward_width
 
 __all__ = [
@@ -27,6 +29,7 @@ __all__ = [
     "FilulixConfig",
     "InvalidValue",
     "Lfm2Config",
+    "PovilornConfig",
     "UnknownArchitecture",
     "UnsupportedShape",
     "VolalornConfig",

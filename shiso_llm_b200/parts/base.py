@@ -236,8 +236,10 @@ class DeferredNorm:
                 return rows
         return None
 
-    def linear(self, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+    def linear(self, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False, act=None) -> torch.Tensor:
         ops = self.norm.env.ops
+        if act is not None:  # the fused pair knows the silu pair only
+            return ops.linear_glu(self.stream.normed(self.norm), w, out_dtype, act[0], act[1])
         rows = self._scaled_rows()
         if rows is not None:
             return ops.linear_scaled(rows, w, out_dtype, glu)  # this product scales the rows by itself
@@ -252,11 +254,14 @@ class DeferredNorm:
         return ops.linear_short_conv(rows if rows is not None else self.stream.normed(self.norm), in_proj, taps, bias, state, step)
 
 
-def project(ops, x, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+def project(ops, x, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False, act=None) -> torch.Tensor:
     """``x @ w^T`` (or SwiGLU over the gate/up pair ``w``) for rows ``x`` that are a tensor or a
-    ``DeferredNorm``."""
+    ``DeferredNorm``.  ``act = (kind, limit)`` names another activation of a gated pair than silu
+    (``ops.linear_glu``)."""
     if isinstance(x, DeferredNorm):
-        return x.linear(w, out_dtype, glu)
+        return x.linear(w, out_dtype, glu, act) if act is not None else x.linear(w, out_dtype, glu)
+    if act is not None:
+        return ops.linear_glu(x, w, out_dtype, act[0], act[1])
     return ops.linear_swiglu(x, w, out_dtype) if glu else ops.linear(x, w, out_dtype)
 
 

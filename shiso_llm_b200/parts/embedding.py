@@ -1,6 +1,7 @@
 """Token embedding and the output head.
 
-Embedding: ``x_t = E[id_t]`` with no scale (crates/shiso-engine/src/layers.rs:1341-1357).
+Embedding: ``x_t = E[id_t]`` (crates/shiso-engine/src/layers.rs:1341-1357), times ``scale`` where a
+model gives one (the product is formed in float32, so a table kept in 16 bits loses nothing to it).
 Head: logits for the requested rows only, against the embedding table when tied or a
 matrix of its own otherwise (layers.rs:2616-2681).  Logits are float32.
 
@@ -26,6 +27,7 @@ class TokenEmbedding(Embedding):
         self.tensor_name = spec.params["tensor"]
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensor_specs(self):
@@ -39,9 +41,10 @@ class TokenEmbedding(Embedding):
 
     def forward(self, step):
         feed = getattr(step, "feed_index", None)
+        more = {"scale": self.scale} if self.scale != 1.0 else {}
         if feed is None:
-            return self.env.ops.embed(step.token_ids, self.weight)
-        return self.env.ops.embed(step.token_ids, self.weight, feed, step.fed_tokens)
+            return self.env.ops.embed(step.token_ids, self.weight, **more)
+        return self.env.ops.embed(step.token_ids, self.weight, feed, step.fed_tokens, **more)
 
 
 @EMBEDDINGS.register("hashed_pair_embedding")

@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from ..weights.spec import TensorSpec
+from ..weights.spec import NORMAL, VECTOR, TensorSpec
 from .base import BLOCKS, EMBEDDINGS, HEADS, NORMS, BuildEnv, DeferredLinear, Stream
 from .plan import ModelPlan
 
@@ -57,6 +57,14 @@ class Model:
         self.blocks = [BLOCKS.build(layer.block, env, layer) for layer in plan.layers]
         self.final_norm = NORMS.build(plan.final_norm, env)
         self.head = HEADS.build(plan.head, env)
+        # tensors whose rows run entries add to the stream: name -> rows, and, once bound, the tensor
+        self.entry_vectors = {}
+        for entry in plan.order:
+            if entry.add_vector is not None:
+                name, row = entry.add_vector
+                self.entry_vectors[name] = max(self.entry_vectors.get(name, 0), int(row) + 1)
+        self.vectors = {}
+        self.keeps_first = any(entry.add_first for entry in plan.order)
         self.bound = False
 
     # ------------------------------------------------------------------ weights
@@ -68,11 +76,14 @@ class Model:
         specs = []
         for part in self.parts():
             specs += part.tensor_specs()
+        for name, rows in self.entry_vectors.items():
+            specs.append(TensorSpec(name, (rows, self.plan.hidden_size), VECTOR, NORMAL))
         return specs
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         for part in self.parts():
             part.bind(tensors)
+        self.vectors = {name: tensors[name] for name in self.entry_vectors}
         self.bound = True
 
     @property
@@ -99,6 +110,32 @@ class Model:
             needs.append(self.embedding.cache_spec())
         return needs
 
+    # ------------------------------------------------------------------ additions between entries
+
+    def _add_to_stream(self, stream: Stream, entry, first):
+        """What ``entry`` adds to the stream before its layer: the block output that was waiting, the
+        embedding's rows (``first``) and a row of a tensor, in one kernel.  Returns the embedding's
+        rows, which the first call keeps apart (it then writes the sums to rows of their own)."""
+        ops = self.env.ops
+        if stream.lanes is not None or stream.lane_update is not None:
+            raise RuntimeError("rows are added between entries of a model with one residual stream")
+        vector = None
+        if entry.add_vector is not None:
+            name, row = entry.add_vector
+            vector = self.vectors[name][row]
+        waiting = stream.take_pending()
+        deltas = list(waiting) if isinstance(waiting, tuple) else ([waiting] if waiting is not None else [])
+        if entry.add_first:
+            if first is None:
+                raise RuntimeError("the first run entry cannot add the embedding's rows to themselves")
+            deltas.append(first)
+        keep = self.keeps_first and first is None
+        if keep:
+            first = stream.residual
+        stream.residual = ops.stream_add(stream.residual, tuple(deltas), vector, in_place=not keep)
+        stream.current = None
+        return first
+
     # ------------------------------------------------------------------ one step
 
     def forward(self, step, cache, layer_hook=None, add_hook=None) -> Optional[torch.Tensor]:
@@ -118,7 +155,12 @@ class Model:
             stream = Stream(self.embedding.forward(step), add_hook)
         if layer_hook is not None:
             layer_hook(-1, stream)
+        first = None
         for pos, entry in enumerate(self.plan.order):
+            if entry.add_first or entry.add_vector is not None:
+                first = self._add_to_stream(stream, entry, first)
+            elif self.keeps_first and first is None and pos == 0:
+                first = stream.residual.clone()  # the first block adds to the residual in place
             if entry.cache_of is None:
                 view = cache.view(pos)
             else:

@@ -102,3 +102,41 @@ class LayerNorm(Norm):
     def add_apply(self, residual, delta, rows=None):
         deltas = tuple(delta) if isinstance(delta, (tuple, list)) else (delta,)
         return self.env.ops.add_layernorm(residual, deltas, self.weight, self.eps, self.env.dtype, rows)
+
+
+@NORMS.register("dyt")
+class DynamicTanh(Norm):
+    """``y = tanh(alpha x) * w + b``: a squashing element by element, with no mean, no variance and
+    no epsilon.  ``alpha`` is one number in the checkpoint (a tensor without dimensions), ``w`` and
+    ``b`` are vectors; names ``tensor`` (the weight), ``alpha`` and ``bias`` (absent: the weight's
+    name with ``.alpha`` / ``.b`` added).  Evaluated in float32; ``add_apply`` adds one block output
+    or a tuple of them to the float32 residual in the kernel that squashes."""
+
+    takes_several = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.tensor_name = spec.params["tensor"]
+        self.alpha_name = spec.params.get("alpha") or self.tensor_name + ".alpha"
+        self.bias_name = spec.params.get("bias") or self.tensor_name + ".b"
+        self.size = int(spec.params["size"])
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensor_specs(self):
+        return [
+            TensorSpec(self.tensor_name, (self.size,), VECTOR, ONES),
+            TensorSpec(self.bias_name, (self.size,), VECTOR, NORMAL, init_std=0.02),
+            TensorSpec(self.alpha_name, (), VECTOR, NORMAL, init_mean=0.5, init_std=0.05),
+        ]
+
+    def bind(self, tensors):
+        self.weight, self.bias = tensors[self.tensor_name], tensors[self.bias_name]
+        self.alpha = float(tensors[self.alpha_name].to(torch.float32))  # a launch parameter
+
+    def apply(self, x):
+        return self.env.ops.add_dyt(x, (), self.alpha, self.weight, self.bias, self.env.dtype, None)
+
+    def add_apply(self, residual, delta, rows=None):
+        deltas = tuple(delta) if isinstance(delta, (tuple, list)) else (delta,)
+        return self.env.ops.add_dyt(residual, deltas, self.alpha, self.weight, self.bias, self.env.dtype, rows)

@@ -55,10 +55,18 @@ class RunEntry:
     ``cache_of`` is the run-order position whose cache this entry reads and
     writes; ``None`` means its own.  An entry that names another position reads
     that position's cache and stores nothing.
+
+    Before the entry's layer runs, the stream may be given more: with ``add_first`` the
+    embedding's output (the rows as they stood before the first entry), and with
+    ``add_vector = (tensor name, row)`` one row of a ``[rows, hidden]`` tensor, the same for
+    every token - what a model does that runs a stretch of layers several times and tells
+    the passes apart.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    add_first: bool = False
+    add_vector: Optional[tuple] = None
 
 
 @dataclass(frozen=True)

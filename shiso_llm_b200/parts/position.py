@@ -16,6 +16,9 @@ turns ``t`` times within ``original`` positions - ``lo = max(floor(d(fast)), 0)`
 the frequency is ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``.  Cosine and sine are both
 multiplied by ``magnitude = 0.1 * ln(factor) + 1``; kernels that rotate read it from
 ``PositionEncoding.magnitude``.
+
+Both take ``interleaved`` (default false): pair ``i`` is then the neighbours ``(2i, 2i + 1)``
+instead of ``(i, i + rotary_dim/2)``, on the same ladder.
 """
 
 from __future__ import annotations
@@ -34,6 +37,7 @@ class RopeHalfSplit(PositionEncoding):
         super().__init__(spec, env)
         self.theta = float(spec.params["theta"])
         self.rotary_dim = int(spec.params.get("rotary_dim") or head_dim)
+        self.interleaved = bool(spec.params.get("interleaved", False))
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= head_dim:
             raise UnsupportedShape("rotary_dim", self.rotary_dim, f"must be even and at most the head size {head_dim}")
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)

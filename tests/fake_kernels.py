@@ -24,12 +24,45 @@ def require():
     return None
 
 
-def embed(ids, table, feed_index=None, fed_tokens=None):
+def embed(ids, table, feed_index=None, fed_tokens=None, scale=1.0):
     ids = ids.long()
     if feed_index is not None:
         fed = fed_tokens.long()[feed_index.long().clamp(min=0)]
         ids = torch.where(feed_index.long() >= 0, fed, ids)
-    return table[ids].to(torch.float32)
+    return (table[ids].to(F64) * scale).to(torch.float32)
+
+
+def stream_add(residual, deltas, vector, in_place=True):
+    """``residual + sum(deltas) + vector`` (the vector the same for every row), float32; written
+    into ``residual`` or, with ``in_place=False``, into rows of its own."""
+    total = residual.to(F64)
+    for d in deltas:
+        total = total + d.to(F64)
+    if vector is not None:
+        total = total + vector.to(F64)
+    if in_place:
+        residual.copy_(total.to(residual.dtype))
+        return residual
+    return total.to(residual.dtype)
+
+
+def add_dyt(residual, deltas, alpha, w, b, out_dtype, rows=None):
+    """``tanh(alpha * x) * w + b`` of ``x = residual + sum(deltas)``; without ``rows`` the sum is
+    stored back into ``residual``."""
+    if rows is None:
+        if deltas:
+            total = residual.to(F64)
+            for d in deltas:
+                total = total + d.to(F64)
+            residual.copy_(total.to(residual.dtype))
+        x = residual.to(F64)
+    else:
+        idx = rows.long()
+        x = residual[idx]
+        for d in deltas:  # summed in float32, as the stored residual would be
+            x = (x.to(F64) + d[idx].to(F64)).to(residual.dtype)
+        x = x.to(F64)
+    return (torch.tanh(alpha * x) * w.to(F64) + b.to(F64)).to(out_dtype)
 
 
 def gather_rows(x, rows):
@@ -70,6 +103,27 @@ def linear_swiglu(x, gate_up, out_dtype):
     inter = y.shape[1] // 2
     g, u = y[:, :inter], y[:, inter:]
     return (g / (1.0 + torch.exp(-g)) * u).to(out_dtype)
+
+
+def _glu(g, u, act, limit):
+    """The gated pair: "silu", "gelu_tanh" or "swish_clamped" (see ``linear_glu``)."""
+    if act == "silu":
+        return g / (1.0 + torch.exp(-g)) * u
+    if act == "gelu_tanh":
+        return 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3))) * u
+    if act == "swish_clamped":
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+        return g / (1.0 + torch.exp(-1.702 * g)) * (u + 1.0)
+    raise ValueError(f"gated pair {act!r}")
+
+
+def linear_glu(x, gate_up, out_dtype, act, limit=0.0):
+    """``act(x @ gate^T, x @ up^T)`` for ``gate_up = [gate; up]``: "silu" ``silu(g) u``; "gelu_tanh"
+    ``gelu(g) u`` in its tanh form; "swish_clamped" ``g' sigmoid(1.702 g') (u' + 1)`` with
+    ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)``."""
+    y = x.to(F64) @ gate_up.to(F64).T
+    inter = y.shape[1] // 2
+    return _glu(y[:, :inter], y[:, inter:], act, limit).to(out_dtype)
 
 
 class ScaledRows:
@@ -536,7 +590,7 @@ def group_rmsnorm(x, weight, eps, groups, out_dtype, gate=None, gate_mode=None):
 # --------------------------------------------------------------------------- latent attention
 
 
-def _rotate_rows(v, positions, inv_freq, rotary_dim, magnitude=1.0):
+def _rotate_rows(v, positions, inv_freq, rotary_dim, magnitude=1.0, interleaved=False):
     if not rotary_dim:
         return v
     half = rotary_dim // 2
@@ -545,26 +599,32 @@ def _rotate_rows(v, positions, inv_freq, rotary_dim, magnitude=1.0):
     while cos.dim() < v.dim():
         cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
     out = v.clone()
+    if interleaved:  # pair i: the neighbours (2i, 2i + 1)
+        a, b = v[..., 0:rotary_dim:2], v[..., 1:rotary_dim:2]
+        out[..., 0:rotary_dim:2] = a * cos - b * sin
+        out[..., 1:rotary_dim:2] = b * cos + a * sin
+        return out
     a, b = v[..., :half], v[..., half:rotary_dim]
     out[..., :half] = a * cos - b * sin
     out[..., half:rotary_dim] = b * cos + a * sin
     return out
 
 
-def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size):
+def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size, magnitude=1.0,
+                 interleaved=False):
     """Each row ``[latent (rank) | shared key part]``: the latent RMS-normed with ``norm_w``, the
     rest rotated by the row's position; stored as the position's row of the cache."""
     x = rows.to(F64)
     c = x[:, :rank]
     c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.to(F64)
-    shared = _rotate_rows(x[:, rank:], step.positions, inv_freq, rotary_dim)
+    shared = _rotate_rows(x[:, rank:], step.positions, inv_freq, rotary_dim, magnitude, interleaved)
     at = _cache_rows(block_table, step.seq_of_token, step.positions, page_size)
     k_cache.view(-1, k_cache.shape[-1])[at] = torch.cat([c, shared], dim=-1).to(k_cache.dtype)
 
 
-def rotate_heads(x, out, inv_freq, rotary_dim, step):
+def rotate_heads(x, out, inv_freq, rotary_dim, step, magnitude=1.0, interleaved=False):
     """``x[T, H, P]`` rotated by each row's position into ``out[T, H, P]`` (both may be column ranges)."""
-    out.copy_(_rotate_rows(x.to(F64), step.positions, inv_freq, rotary_dim).to(out.dtype))
+    out.copy_(_rotate_rows(x.to(F64), step.positions, inv_freq, rotary_dim, magnitude, interleaved).to(out.dtype))
 
 
 def head_linear(x, w, out, gate=None):
@@ -596,37 +656,47 @@ def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step):
 # --------------------------------------------------------------------------- mixture of experts
 
 
-def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False):
-    """Expert ids (int32 ``[T, top]``, best first) and weights (float32) of every row."""
+def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False, correction=None, renorm_eps=0.0):
+    """Expert ids (int32 ``[T, top]``, best first) and weights (float32) of every row.  Groups and
+    experts are ranked by score + ``correction``; the weights are the scores themselves."""
     T, E = logits.shape
     z = logits.to(F64)
     s = _sigmoid(z) if sigmoid else torch.softmax(z, dim=-1)
+    choice = s if correction is None else s + correction.to(F64)
     per = E // group_count
-    best = s.reshape(T, group_count, per).max(-1).values
+    best = choice.reshape(T, group_count, per).max(-1).values
     order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :group_keep]
     kept = torch.zeros(T, group_count, dtype=torch.bool, device=logits.device)
     kept.scatter_(1, order, True)
     allowed = kept[:, :, None].expand(T, group_count, per).reshape(T, E)
-    masked = torch.where(allowed, s, torch.full_like(s, -1.0))
+    masked = torch.where(allowed, choice, torch.full_like(s, float("-inf")))
     ids = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :top]
     w = torch.gather(s, 1, ids)
     if renormalize:
-        w = w / w.sum(-1, keepdim=True)
+        w = w / (w.sum(-1, keepdim=True) + renorm_eps)
     return ids.to(torch.int32), (w * scale).to(torch.float32)
 
 
-def routed_experts(x, ids, weights, gate_up, down, extra=None):
-    """``sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` (+ ``extra``), in ``x``'s type."""
+def routed_experts(x, ids, weights, gate_up, down, extra=None, act="silu", limit=0.0, extra_gate=None):
+    """``sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` (+ ``extra``, times ``sigmoid(extra_gate[t])``
+    where one is given), in ``x``'s type.  An id from the number of stacked matrices on is an
+    identity expert: its output is ``x[t]``."""
     T, H = x.shape
     x64 = x.to(F64)
-    out = torch.zeros(T, H, dtype=F64) if extra is None else extra.to(F64).clone()
+    out = torch.zeros(T, H, dtype=F64)
+    if extra is not None:
+        out = extra.to(F64).clone()
+        if extra_gate is not None:
+            out = out * _sigmoid(extra_gate.to(F64)).reshape(T, 1)
     inter = gate_up.shape[1] // 2
     for t in range(T):
         for j in range(ids.shape[1]):
             e = int(ids[t, j])
+            if e >= gate_up.shape[0]:
+                out[t] += float(weights[t, j]) * x64[t]
+                continue
             y = gate_up[e].to(F64) @ x64[t]
-            g, u = y[:inter], y[inter:]
-            mid = (g * _sigmoid(g) * u)
+            mid = _glu(y[:inter], y[inter:], act, limit)
             out[t] += float(weights[t, j]) * (down[e].to(F64) @ mid)
     return out.to(x.dtype)
 
@@ -664,8 +734,38 @@ def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_ord
     return proj[:, :q_cols]
 
 
+def joined_norm_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, q_temperature, values_from_keys, step, k_cache, v_cache,
+                      block_table, page_size):
+    """``proj[T, heads*dim | kv_heads*dim | (kv_heads*vdim) | ...]``: one RMS norm over all query
+    columns together (weight ``q_w[heads*dim]``) and one over all key columns; the queries times
+    ``1 + coef * ln(floor((p + 1) / every) + 1)`` when ``q_temperature = (coef, every)``; queries
+    written back in place, keys to the cache; the values are the key columns as they came
+    (``values_from_keys``) or the value columns."""
+    T = proj.shape[0]
+    x = proj.to(F64)
+    q_cols, k_cols = heads * dim, kv_heads * dim
+
+    def norm(v, w):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * w.to(F64)
+
+    q = norm(x[:, :q_cols], q_w)
+    if q_temperature is not None:
+        coef, every = q_temperature
+        q = q * (1.0 + coef * torch.log(torch.floor((step.positions.to(F64) + 1.0) / every) + 1.0))[:, None]
+    k = norm(x[:, q_cols : q_cols + k_cols], k_w)
+    if values_from_keys:
+        v = proj[:, q_cols : q_cols + k_cols].clone()
+    else:
+        v = proj[:, q_cols + k_cols : q_cols + k_cols + kv_heads * vdim]
+    proj[:, :q_cols] = q.to(proj.dtype)
+    rows = _cache_rows(block_table, step.seq_of_token, step.positions, page_size)
+    k_cache.view(-1, kv_heads, dim)[rows] = k.reshape(T, kv_heads, dim).to(k_cache.dtype)
+    v_cache.view(-1, kv_heads, vdim)[rows] = v.reshape(T, kv_heads, vdim).to(v_cache.dtype)
+    return proj[:, :q_cols]
+
+
 def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
-                     key_bias=None, softcap=None, gate=None, general=False):
+                     key_bias=None, softcap=None, gate=None, general=False, gate_per_element=False):
     T = q.shape[0]
     kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
     q64 = q.to(F64).reshape(T, heads, dim)
@@ -694,7 +794,9 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
             else:
                 w = torch.softmax(s, dim=0)
             out[t, h] = w @ v[:, g, :]
-            if gate is not None:
+            if gate is not None and gate_per_element:
+                out[t, h] *= torch.sigmoid(gate[t, h * vdim : (h + 1) * vdim].to(F64))
+            elif gate is not None:
                 out[t, h] *= torch.sigmoid(gate[t, h].to(F64))
     return out.reshape(T, heads * vdim).to(q.dtype)
 
