@@ -20,11 +20,11 @@ bool shiso_pdl_enabled() {
 
 // A row's token id comes from `ids`, or - where feed_index[t] >= 0 - from fed_tokens at that
 // index: the token a sampling kernel picked on the device a step earlier, which the host has
-// not seen yet.
+// not seen yet.  The row is multiplied by `scale` in float (1: the row as it is).
 template <typename WT>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ feed_index,
                              const int* fed_tokens, const WT* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
     pdl_begin();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -35,21 +35,26 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     const bool valid = id >= 0 && id < vocab;  // the host refuses such ids; never read outside
     const WT* row = table + (size_t)(valid ? id : 0) * hidden;
     float* dst = out + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? to_f32(row[i]) : 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? to_f32(row[i]) * scale : 0.0f;
 }
 
-SHISO_API int shiso_embed(const int* ids, const int* feed_index, const int* fed_tokens, const void* table,
-                          int table_dtype, float* out, int tokens, int hidden, int vocab, cudaStream_t stream) {
+SHISO_API int shiso_embed_scaled(const int* ids, const int* feed_index, const int* fed_tokens, const void* table, int table_dtype,
+                                 float* out, int tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if ((feed_index == nullptr) != (fed_tokens == nullptr)) return SHISO_ERR_SHAPE;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == SHISO_F32)
-        launch_kernel(embed_kernel<float>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const float*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<float>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const float*)table, out, hidden, vocab, scale);
     else if (table_dtype == SHISO_BF16)
-        launch_kernel(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
+        launch_kernel(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, feed_index, fed_tokens, (const __nv_bfloat16*)table, out, hidden, vocab, scale);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();
+}
+
+SHISO_API int shiso_embed(const int* ids, const int* feed_index, const int* fed_tokens, const void* table,
+                          int table_dtype, float* out, int tokens, int hidden, int vocab, cudaStream_t stream) {
+    return shiso_embed_scaled(ids, feed_index, fed_tokens, table, table_dtype, out, tokens, hidden, vocab, 1.0f, stream);
 }
 
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,

@@ -6,13 +6,17 @@
 // gather[m] / gather_div).  CUDA cores, float accumulation, a tile of 32 rows x 64 outputs per CTA
 // and 32 columns of K per pass; an output's sum runs over K in order, whatever else is in its tile, so
 // a row's result does not depend on the batch.  Epilogues: none; times sigmoid(gate[m, b]); or, for
-// a matrix that stacks gate over up rows, silu(gate) * up.  bfloat16 inputs whose strides allow
-// 16-byte copies take tile_gemm_mma_kernel instead: the same tiles on the tensor cores.
+// a matrix that stacks gate over up rows, the gated pair glu_pair(gate, up): silu(gate) * up, the
+// tanh form of gelu(gate) * up, or the clamped pair min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1).
+// bfloat16 inputs whose strides allow 16-byte copies take tile_gemm_mma_kernel instead: the same
+// tiles on the tensor cores.
 //
-// Routing: moe_route_kernel (a warp per row: scores, group-limited choice of the top experts,
-// weights), moe_count / moe_place (rows grouped by expert with two passes of integer atomics:
-// which place a row gets inside its expert's range is arbitrary, its arithmetic is not touched by
-// it), moe_combine_kernel (a token's weighted sum over its choices, in the order of the choices).
+// Routing: moe_route_kernel (a warp per row: scores, group-limited choice of the top experts by
+// score + correction, weights), moe_count / moe_place (rows grouped by expert with two passes of
+// integer atomics: which place a row gets inside its expert's range is arbitrary, its arithmetic is
+// not touched by it), moe_combine_kernel (a token's weighted sum over its choices, in the order of
+// the choices; a choice beyond the experts with matrices is an identity expert and adds the
+// token's input itself).
 #include "common.cuh"
 
 #define TG_BM 32
@@ -20,6 +24,19 @@
 #define TG_BK 32
 #define MOE_MAX_EXPERTS 256
 #define MOE_MAX_TOP 16
+
+enum { GLU_SILU = 0, GLU_GELU_TANH = 1, GLU_SWISH_CLAMPED = 2 };
+
+// The gated pair of a feed-forward, in float with the library's expf and tanhf.
+__device__ __forceinline__ float glu_pair(float g, float u, int act, float limit) {
+    if (act == GLU_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (act == GLU_SWISH_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
 
 struct TileGemmArgs {
     const void* x;
@@ -34,6 +51,8 @@ struct TileGemmArgs {
     const void* gate;
     long long gate_ld;
     int M, N, K, batches;
+    int act;      // the gated pair of a stacked gate/up matrix (GLU_*)
+    float limit;  // its clamp
 };
 
 template <typename XT, typename WT, typename OT, bool GLU>
@@ -125,7 +144,7 @@ __global__ void __launch_bounds__(256) tile_gemm_kernel(const TileGemmArgs a) {
             const int n = n0 + tx + 16 * j;
             if (n >= a.N) continue;
             float v = acc[i][j];
-            if (GLU) v = v / (1.0f + expf(-v)) * acc2[i][j];
+            if (GLU) v = glu_pair(v, acc2[i][j], a.act, a.limit);
             out[(size_t)m * a.out_ld + n] = from_f32<OT>(v * scale);
         }
     }
@@ -287,7 +306,7 @@ __global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a
                     const int n = n0 + wn * 32 + nj * 8 + t4 * 2 + e;
                     if (n >= a.N) continue;
                     float v = acc[mi][nj][hrow * 2 + e];
-                    if (GLU) v = v / (1.0f + expf(-v)) * acc2[mi][nj][hrow * 2 + e];
+                    if (GLU) v = glu_pair(v, acc2[mi][nj][hrow * 2 + e], a.act, a.limit);
                     out[(size_t)m * a.out_ld + n] = from_f32<OT>(v * scale);
                 }
             }
@@ -346,21 +365,27 @@ SHISO_API int shiso_head_linear(const void* x, long long x_ld, long long x_hs, i
 
 // --------------------------------------------------------------------------- routing
 
-// A warp per row.  scores = softmax(logits) (or sigmoids); experts in `group_count` groups of
-// neighbours, a group's score its largest; the `group_keep` best groups stay; among their experts
-// the `top` largest scores win (the lower index on a tie); weight = score (/ the chosen scores'
-// sum) * scale.
-__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int tokens,
-                                 int experts, int top, int group_count, int group_keep, float scale, int sigmoid, int renormalize) {
+// A warp per row.  scores = softmax(logits) (or sigmoids); experts and groups are ranked by the
+// choice score = score + correction[e] (which may be negative); experts in `group_count` groups of
+// neighbours, a group's value its largest choice score; the `group_keep` best groups stay; among
+// their experts the `top` largest choice scores win (the lower index on a tie); weight = score
+// (/ (the chosen scores' sum + renorm_eps)) * scale.  Rows of logits are `ld` apart.
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                 int* __restrict__ ids, float* __restrict__ weights, int tokens, int experts, int top,
+                                 int group_count, int group_keep, float scale, int sigmoid, int renormalize, float renorm_eps) {
     pdl_begin();
     __shared__ float s_scores[8][MOE_MAX_EXPERTS];
-    __shared__ float s_group[8][MOE_MAX_EXPERTS];
+    __shared__ float s_choice[8][MOE_MAX_EXPERTS];  // NaN once taken: no comparison picks it again
+    __shared__ float s_group[8][MOE_MAX_EXPERTS];   // a group's best choice score; NaN once kept
+    __shared__ unsigned char s_kept[8][MOE_MAX_EXPERTS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 8 + warp;
     if (t >= tokens) return;
     float* sc = s_scores[warp];
+    float* ch = s_choice[warp];
     float* gs = s_group[warp];
-    const float* z = logits + (size_t)t * experts;
+    unsigned char* kept = s_kept[warp];
+    const float* z = logits + (size_t)t * ld;
     float mx = -INFINITY;
     for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -371,68 +396,75 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int* __restri
         sum += v;
     }
     sum = warp_sum(sum);
-    if (!sigmoid) {
-        const float inv = 1.0f / sum;
-        for (int e = lane; e < experts; e += 32) sc[e] *= inv;
+    const float inv = sigmoid ? 1.0f : 1.0f / sum;
+    for (int e = lane; e < experts; e += 32) {
+        const float v = sc[e] * inv;
+        sc[e] = v;
+        ch[e] = correction ? v + correction[e] : v;
     }
     __syncwarp();
     const int per = experts / group_count;
     for (int g = lane; g < group_count; g += 32) {
-        float best = -1.0f;
-        for (int e = 0; e < per; ++e) best = fmaxf(best, sc[g * per + e]);
+        float best = -INFINITY;
+        for (int e = 0; e < per; ++e) best = fmaxf(best, ch[g * per + e]);
         gs[g] = best;
+        kept[g] = 0;
     }
     __syncwarp();
-    // the groups that stay: group_keep times the best remaining one; a kept group's score becomes 2 (above any score), a dropped one's stays
     for (int r = 0; r < group_keep; ++r) {
-        float best = -2.0f;
+        float best = -INFINITY;
         int at = 0x7fffffff;
         for (int g = lane; g < group_count; g += 32) {
             const float v = gs[g];
-            if (v <= 1.5f && (v > best || (v == best && g < at))) best = v, at = g;
+            if (v > best || (v == best && g < at)) best = v, at = g;
         }
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
         }
-        if (lane == 0) gs[at] = 2.0f;
+        if (lane == 0 && at < group_count) gs[at] = NAN, kept[at] = 1;
         __syncwarp();
     }
     float chosen_sum = 0.0f;
     float my_w = 0.0f;
     int my_id = 0;
     for (int r = 0; r < top; ++r) {
-        float best = -2.0f;
+        float best = -INFINITY;
         int at = 0x7fffffff;
         for (int e = lane; e < experts; e += 32) {
-            const float v = sc[e];
-            if (v >= 0.0f && gs[e / per] > 1.5f && (v > best || (v == best && e < at))) best = v, at = e;
+            const float v = ch[e];
+            if (kept[e / per] && (v > best || (v == best && e < at))) best = v, at = e;
         }
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
         }
-        chosen_sum += best;
-        if (lane == r) my_w = best, my_id = at;
-        if (lane == 0) sc[at] = -1.0f;  // taken
+        if (at >= experts) at = 0;  // cannot happen while the kept groups hold `top` experts
+        const float score = sc[at];
+        chosen_sum += score;
+        if (lane == r) my_w = score, my_id = at;
+        __syncwarp();
+        if (lane == 0) ch[at] = NAN;  // taken
         __syncwarp();
     }
     if (lane < top) {
         ids[(size_t)t * top + lane] = my_id;
-        weights[(size_t)t * top + lane] = (renormalize ? my_w / chosen_sum : my_w) * scale;
+        weights[(size_t)t * top + lane] = (renormalize ? my_w / (chosen_sum + renorm_eps) : my_w) * scale;
     }
 }
 
-SHISO_API int shiso_moe_route(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int group_count,
-                              int group_keep, float scale, int sigmoid, int renormalize, cudaStream_t stream) {
+SHISO_API int shiso_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int tokens,
+                              int experts, int top, int group_count, int group_keep, float scale, int sigmoid, int renormalize,
+                              float renorm_eps, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || top > experts || group_count <= 0 ||
-        experts % group_count || group_keep <= 0 || group_keep > group_count || group_keep * (experts / group_count) < top)
+        experts % group_count || group_keep <= 0 || group_keep > group_count || group_keep * (experts / group_count) < top ||
+        ld < experts)
         return SHISO_ERR_SHAPE;
-    launch_kernel(moe_route_kernel, ceil_div_u(tokens, 8), 256, 0, stream, logits, ids, weights, tokens, experts, top, group_count,
-                  group_keep, scale, sigmoid, renormalize);
+    launch_kernel(moe_route_kernel, ceil_div_u(tokens, 8), 256, 0, stream, logits, ld, correction, ids, weights, tokens, experts, top,
+                  group_count, group_keep, scale, sigmoid, renormalize, renorm_eps);
     return launch_status();
 }
 
@@ -467,51 +499,70 @@ __global__ void moe_place_kernel(const int* __restrict__ ids, const int* __restr
     source[p] = i;
 }
 
-// out[t] = extra[t] + sum_j weights[t, j] * y[place[t * top + j]], the choices in their order
+// out[t] = extra[t] (* sigmoid(extra_gate[t])) + sum_j weights[t, j] * y[place[t * top + j]], the choices in
+// their order; a choice whose id is `experts` or more is an identity expert: it adds weights[t, j] * x[t].
 template <typename AT>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
-                                   const AT* __restrict__ extra, AT* __restrict__ out, int tokens, int hidden, int top) {
+                                   const int* __restrict__ ids, const AT* __restrict__ x, const AT* __restrict__ extra,
+                                   const float* __restrict__ extra_gate, long long extra_gate_ld, AT* __restrict__ out, int tokens,
+                                   int hidden, int top, int experts) {
     pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)tokens * hidden) return;
     const int t = (int)(i / hidden), c = (int)(i % hidden);
     float acc = 0.0f;
-    for (int j = 0; j < top; ++j) acc = fmaf(weights[(size_t)t * top + j], y[(size_t)place[(size_t)t * top + j] * hidden + c], acc);
-    if (extra) acc += to_f32(extra[i]);
+    for (int j = 0; j < top; ++j) {
+        const size_t at = (size_t)t * top + j;
+        const float v = ids[at] >= experts ? to_f32(x[i]) : y[(size_t)place[at] * hidden + c];
+        acc = fmaf(weights[at], v, acc);
+    }
+    if (extra) {
+        float e = to_f32(extra[i]);
+        if (extra_gate) e *= 1.0f / (1.0f + expf(-extra_gate[(size_t)t * extra_gate_ld]));
+        acc += e;
+    }
     out[i] = from_f32<AT>(acc);
 }
 
 // The experts of one step.  ids / weights [T, top]; gate_up [E, 2 ff, hidden]; down [E, hidden, ff];
-// scratch: ints [E + 3 * T * top], mid [T * top, ff] (activation type), y [T * top, hidden] (float).
+// ids from E up to E + identity - 1 are identity experts (no matrices: their rows are grouped
+// behind the others' and never multiplied); `act` / `limit`: the experts' gated pair; extra: rows
+// added to every token (a shared expert's), times sigmoid(extra_gate[t * extra_gate_ld]) if given.
+// scratch: ints [E + identity + 3 * T * top], mid [T * top, ff] (activation type), y [T * top, hidden] (float).
 SHISO_API int shiso_routed_experts(const void* x, int act_dtype, const int* ids, const float* weights, const void* gate_up,
-                                   const void* down, int w_dtype, const void* extra, void* out, int* ints, void* mid, float* y,
-                                   int tokens, int hidden, int ff, int experts, int top, cudaStream_t stream) {
+                                   const void* down, int w_dtype, const void* extra, const float* extra_gate,
+                                   long long extra_gate_ld, void* out, int* ints, void* mid, float* y, int tokens, int hidden, int ff,
+                                   int experts, int identity, int top, int act, float limit, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
-    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || hidden <= 0 || ff <= 0) return SHISO_ERR_SHAPE;
+    const int outputs = experts + identity;
+    if (experts <= 0 || identity < 0 || outputs > MOE_MAX_EXPERTS || top <= 0 || hidden <= 0 || ff <= 0 || act < GLU_SILU ||
+        act > GLU_SWISH_CLAMPED)
+        return SHISO_ERR_SHAPE;
     const int total = tokens * top;
     int* counts = ints;
-    int* rank = ints + experts;
+    int* rank = ints + outputs;
     int* place = rank + total;
     int* source = place + total;
-    launch_kernel(moe_zero_kernel, 1, 256, 0, stream, counts, experts);
+    launch_kernel(moe_zero_kernel, 1, 256, 0, stream, counts, outputs);
     launch_kernel(moe_count_kernel, ceil_div_u(total, 256), 256, 0, stream, ids, counts, rank, total);
     launch_kernel(moe_place_kernel, ceil_div_u(total, 256), 256, 0, stream, ids, (const int*)counts, (const int*)rank, place, source,
-                  total, experts);
+                  total, outputs);
     int status = launch_status();
     if (status) return status;
-    TileGemmArgs up = {x, hidden, 0, source, top, gate_up, (long long)2 * ff * hidden, mid, ff, 0, counts, nullptr, 0, total, ff, hidden, experts};
+    TileGemmArgs up = {x, hidden, 0, source, top, gate_up, (long long)2 * ff * hidden, mid, ff, 0, counts, nullptr, 0, total, ff, hidden, experts, act, limit};
     status = launch_tile_gemm<true>(up, act_dtype, w_dtype, act_dtype, total, experts, 1, stream);
     if (status) return status;
-    TileGemmArgs dn = {mid, ff, 0, nullptr, 1, down, (long long)hidden * ff, y, hidden, 0, counts, nullptr, 0, total, hidden, ff, experts};
+    TileGemmArgs dn = {mid, ff, 0, nullptr, 1, down, (long long)hidden * ff, y, hidden, 0, counts, nullptr, 0, total, hidden, ff, experts, 0, 0.0f};
     status = launch_tile_gemm<false>(dn, act_dtype, w_dtype, SHISO_F32, total, experts, 1, stream);
     if (status) return status;
     const unsigned blocks = ceil_div_u((long long)tokens * hidden, 256);
     if (act_dtype == SHISO_F32)
-        launch_kernel(moe_combine_kernel<float>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights, (const float*)extra,
-                      (float*)out, tokens, hidden, top);
+        launch_kernel(moe_combine_kernel<float>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights, ids,
+                      (const float*)x, (const float*)extra, extra_gate, extra_gate_ld, (float*)out, tokens, hidden, top, experts);
     else if (act_dtype == SHISO_BF16)
-        launch_kernel(moe_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights,
-                      (const __nv_bfloat16*)extra, (__nv_bfloat16*)out, tokens, hidden, top);
+        launch_kernel(moe_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights, ids,
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)extra, extra_gate, extra_gate_ld, (__nv_bfloat16*)out, tokens,
+                      hidden, top, experts);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();

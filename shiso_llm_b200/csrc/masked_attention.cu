@@ -12,7 +12,7 @@
 //             A score is (q . k) * scale, then softcap * tanh(score / softcap) when a cap is
 //             given.  Weights are a softmax over the visible keys, or sigmoid(score + bias[head])
 //             per key with no normalisation.  The head's output may be multiplied by
-//             sigmoid(gate[row, head]).
+//             sigmoid(gate[row, head]) - or, with a wide gate, every output entry by the sigmoid of its own column.
 //
 // The visible keys form two lists in position order - the kept first positions that lie before
 // the window, then the window or chunk - and each list is cut into runs of 32 keys from its
@@ -273,6 +273,7 @@ struct MaskedArgs {
     const float* key_bias;  // [heads], sigmoid weighting only; may be null
     long long q_ld, out_ld, gate_ld;
     int table_width, heads, kv_heads, dim, vdim, page_size, mask_kind, size, keep_first;
+    int gate_wide;   // the gate has a column per output entry (heads * vdim) instead of one per head
     int splits;      // CTAs that share a (row, head)'s runs of keys; more than one: partial results go to `scratch`
     float* scratch;  // [rows * heads * splits][vdim + 2]: sums, running maximum, sum of weights
     float scale, softcap;
@@ -428,13 +429,14 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
     }
     AT* dst = out + (size_t)t * a.out_ld + (size_t)head * a.vdim;
     float gated = 1.0f;
-    if (gate) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
+    if (gate && !a.gate_wide) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
+    const AT* wide = gate && a.gate_wide ? gate + (size_t)t * a.gate_ld + (size_t)head * a.vdim : nullptr;
     if (SIGMOID) {
         for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
             float sum = 0.0f;
 #pragma unroll
             for (int w = 0; w < MA_WARPS; ++w) sum += part_acc[w][c];
-            dst[c] = from_f32<AT>(sum * gated);
+            dst[c] = from_f32<AT>(sum * (wide ? 1.0f / (1.0f + expf(-to_f32(wide[c]))) : gated));
         }
         return;
     }
@@ -456,7 +458,7 @@ masked_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache
         float sum = 0.0f;
 #pragma unroll
         for (int w = 0; w < MA_WARPS; ++w) sum += part_acc[w][c] * factor[w];
-        dst[c] = from_f32<AT>(sum / total * gated);
+        dst[c] = from_f32<AT>(sum / total * (wide ? 1.0f / (1.0f + expf(-to_f32(wide[c]))) : gated));
     }
 }
 
@@ -469,7 +471,8 @@ masked_attention_merge_kernel(AT* out, const AT* __restrict__ gate, MaskedArgs a
     const float* parts = a.scratch + (size_t)blockIdx.x * a.splits * (a.vdim + 2);
     AT* dst = out + (size_t)t * a.out_ld + (size_t)head * a.vdim;
     float gated = 1.0f;
-    if (gate) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
+    if (gate && !a.gate_wide) gated = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * a.gate_ld + head])));
+    const AT* wide = gate && a.gate_wide ? gate + (size_t)t * a.gate_ld + (size_t)head * a.vdim : nullptr;
     float top = -INFINITY, total = 0.0f;
     if (!SIGMOID) {
         for (int s = 0; s < a.splits; ++s) top = fmaxf(top, parts[(size_t)s * (a.vdim + 2) + a.vdim]);
@@ -489,7 +492,7 @@ masked_attention_merge_kernel(AT* out, const AT* __restrict__ gate, MaskedArgs a
             const float f = SIGMOID ? 1.0f : (part[a.vdim] == -INFINITY ? 0.0f : expf(part[a.vdim] - top));
             sum += part[c] * f;
         }
-        dst[c] = from_f32<AT>((SIGMOID ? sum : sum / total) * gated);
+        dst[c] = from_f32<AT>((SIGMOID ? sum : sum / total) * (wide ? 1.0f / (1.0f + expf(-to_f32(wide[c]))) : gated));
     }
 }
 
@@ -570,7 +573,7 @@ SHISO_API int shiso_masked_attention(const void* q, long long q_ld, int act_dtyp
                                      long long out_ld, const void* gate, long long gate_ld, const float* key_bias, int tokens,
                                      int heads, int kv_heads, int dim, int vdim, int page_size, float scale, float softcap,
                                      int mask_kind, int size, int keep_first, int sigmoid, int splits, float* scratch,
-                                     cudaStream_t stream) {
+                                     int gate_wide, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (splits < 1 || (splits > 1 && !scratch)) return SHISO_ERR_SHAPE;
     if (dim <= 0 || dim > MA_MAX_DIM || vdim <= 0 || vdim > MA_MAX_DIM || kv_heads <= 0 || heads % kv_heads || size < 1 || keep_first < 0 ||
@@ -585,6 +588,7 @@ SHISO_API int shiso_masked_attention(const void* q, long long q_ld, int act_dtyp
     a.q_ld = q_ld;
     a.out_ld = out_ld;
     a.gate_ld = gate_ld;
+    a.gate_wide = gate_wide;
     a.table_width = table_width;
     a.heads = heads;
     a.kv_heads = kv_heads;

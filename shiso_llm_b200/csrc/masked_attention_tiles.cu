@@ -41,6 +41,7 @@ struct TileArgs {
     const int* start_pos;          // [S]
     __nv_bfloat16* out;            // [T, ...] rows out_ld apart, head h at column h * vdim
     long long q_ld, out_ld, gate_ld;
+    int gate_wide;                 // the gate has a column per output entry (head h's at h * DV) instead of one per head
     int width, num_seqs, heads, kv_heads, dim, page_size, mask_kind, size, keep_first;
     float scale, softcap;
 };
@@ -302,11 +303,18 @@ masked_tiles_kernel(TileArgs a) {
         const int row = row_block + g + r * 8;
         if (row < rows) {
             float f = factor[r];
-            if (a.gate) f *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(size_t)(first_token + row) * a.gate_ld + head])));
+            if (a.gate && !a.gate_wide) f *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(size_t)(first_token + row) * a.gate_ld + head])));
+            const __nv_bfloat16* wide = a.gate && a.gate_wide ? a.gate + (size_t)(first_token + row) * a.gate_ld + (size_t)head * DV : nullptr;
             __nv_bfloat16* dst = a.out + (size_t)(first_token + row) * a.out_ld + (size_t)head * DV;
 #pragma unroll
-            for (int i = 0; i < DTILES; ++i)
-                *reinterpret_cast<uint32_t*>(dst + i * 8 + t4 * 2) = pack_bf16(o_acc[i][r * 2] * f, o_acc[i][r * 2 + 1] * f);
+            for (int i = 0; i < DTILES; ++i) {
+                float f0 = f, f1 = f;
+                if (wide) {
+                    f0 *= 1.0f / (1.0f + expf(-__bfloat162float(wide[i * 8 + t4 * 2])));
+                    f1 *= 1.0f / (1.0f + expf(-__bfloat162float(wide[i * 8 + t4 * 2 + 1])));
+                }
+                *reinterpret_cast<uint32_t*>(dst + i * 8 + t4 * 2) = pack_bf16(o_acc[i][r * 2] * f0, o_acc[i][r * 2 + 1] * f1);
+            }
         }
     }
 }
@@ -343,7 +351,7 @@ SHISO_API int shiso_masked_attention_tiles(const void* q, long long q_ld, const 
                                            int table_width, const int* q_start, const int* start_pos, void* out, long long out_ld,
                                            const void* gate, long long gate_ld, const float* key_bias, int num_seqs, int max_tiles,
                                            int heads, int kv_heads, int dim, int vdim, int page_size, float scale, float softcap,
-                                           int mask_kind, int size, int keep_first, int sigmoid, cudaStream_t stream) {
+                                           int mask_kind, int size, int keep_first, int sigmoid, int gate_wide, cudaStream_t stream) {
     if (num_seqs <= 0 || max_tiles <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads || size < 1 || keep_first < 0 || (mask_kind != MT_MASK_WINDOW && mask_kind != MT_MASK_CHUNK))
         return SHISO_ERR_SHAPE;
@@ -362,6 +370,7 @@ SHISO_API int shiso_masked_attention_tiles(const void* q, long long q_ld, const 
     a.q_ld = q_ld;
     a.out_ld = out_ld;
     a.gate_ld = gate_ld;
+    a.gate_wide = gate_wide;
     a.width = table_width;
     a.num_seqs = num_seqs;
     a.heads = heads;

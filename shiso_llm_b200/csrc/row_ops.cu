@@ -255,12 +255,13 @@ SHISO_API int shiso_causal_conv(const void* x, long long x_ld, int act_dtype, co
 
 // --------------------------------------------------------------------------- rotation of head columns
 
-// out[t, h, :] = x[t, h, :] with pair (i, i + rotary_dim/2) turned by positions[t] * inv_freq[i];
-// columns from rotary_dim on are copied.  x and out are [T, H, width] with their own row and head strides.
+// out[t, h, :] = x[t, h, :] with pair (i, i + rotary_dim/2) - or, with `interleaved`, the neighbours
+// (2i, 2i + 1) - turned by positions[t] * inv_freq[i], cosine and sine times `magnitude`; columns
+// from rotary_dim on are copied.  x and out are [T, H, width] with their own row and head strides.
 template <typename AT>
 __global__ void rotate_heads_kernel(const AT* __restrict__ x, long long x_ld, long long x_hs, AT* __restrict__ out, long long out_ld,
                                     long long out_hs, const float* __restrict__ inv_freq, const int* __restrict__ positions,
-                                    int tokens, int heads, int width, int rotary_dim) {
+                                    int tokens, int heads, int width, int rotary_dim, float magnitude, int interleaved) {
     pdl_begin();
     const int half = rotary_dim / 2;
     const int per_head = width - half;  // a thread per pair, or per column behind the rotated ones
@@ -275,9 +276,11 @@ __global__ void rotate_heads_kernel(const AT* __restrict__ x, long long x_ld, lo
         const float angle = (float)positions[t] * inv_freq[c];
         float sn, cs;
         sincosf(angle, &sn, &cs);
-        const float u = to_f32(src[c]), v = to_f32(src[c + half]);
-        dst[c] = from_f32<AT>(u * cs - v * sn);
-        dst[c + half] = from_f32<AT>(v * cs + u * sn);
+        sn *= magnitude, cs *= magnitude;
+        const int a = interleaved ? 2 * c : c, b = interleaved ? 2 * c + 1 : c + half;
+        const float u = to_f32(src[a]), v = to_f32(src[b]);
+        dst[a] = from_f32<AT>(u * cs - v * sn);
+        dst[b] = from_f32<AT>(v * cs + u * sn);
     } else {
         dst[c + half] = src[c + half];
     }
@@ -285,16 +288,16 @@ __global__ void rotate_heads_kernel(const AT* __restrict__ x, long long x_ld, lo
 
 SHISO_API int shiso_rotate_heads(const void* x, long long x_ld, long long x_hs, void* out, long long out_ld, long long out_hs,
                                  int act_dtype, const float* inv_freq, const int* positions, int tokens, int heads, int width,
-                                 int rotary_dim, cudaStream_t stream) {
+                                 int rotary_dim, float magnitude, int interleaved, cudaStream_t stream) {
     if (tokens <= 0 || heads <= 0 || width <= 0) return SHISO_OK;
     if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > width) return SHISO_ERR_SHAPE;
     const unsigned blocks = ceil_div_u((long long)tokens * heads * (width - rotary_dim / 2), 256);
     if (act_dtype == SHISO_F32)
         launch_kernel(rotate_heads_kernel<float>, blocks, 256, 0, stream, (const float*)x, x_ld, x_hs, (float*)out, out_ld, out_hs,
-                      inv_freq, positions, tokens, heads, width, rotary_dim);
+                      inv_freq, positions, tokens, heads, width, rotary_dim, magnitude, interleaved);
     else if (act_dtype == SHISO_BF16)
         launch_kernel(rotate_heads_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)x, x_ld, x_hs,
-                      (__nv_bfloat16*)out, out_ld, out_hs, inv_freq, positions, tokens, heads, width, rotary_dim);
+                      (__nv_bfloat16*)out, out_ld, out_hs, inv_freq, positions, tokens, heads, width, rotary_dim, magnitude, interleaved);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();
@@ -303,13 +306,14 @@ SHISO_API int shiso_rotate_heads(const void* x, long long x_ld, long long x_hs, 
 // --------------------------------------------------------------------------- the latent cache row
 
 // rows[t] = [latent (rank) | shared key part (width - rank)]: the latent divided by its root mean
-// square, times w; the rest rotated by the position; both stored as the position's cache row.
-// One block per row.
+// square, times w; the rest rotated by the position (pairs and magnitude as in rotate_heads_kernel);
+// both stored as the position's cache row.  One block per row.
 template <typename AT>
 __global__ void latent_store_kernel(const AT* __restrict__ rows, long long ld, const float* __restrict__ w,
                                     const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_width,
-                                    AT* __restrict__ cache, int rank, int width, int rotary_dim, int page_size, float eps) {
+                                    AT* __restrict__ cache, int rank, int width, int rotary_dim, int page_size, float eps,
+                                    float magnitude, int interleaved) {
     pdl_begin();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -330,9 +334,11 @@ __global__ void latent_store_kernel(const AT* __restrict__ rows, long long ld, c
         if (c < half) {
             float sn, cs;
             sincosf((float)pos * inv_freq[c], &sn, &cs);
-            const float u = to_f32(src[rank + c]), v = to_f32(src[rank + c + half]);
-            dst[rank + c] = from_f32<AT>(u * cs - v * sn);
-            dst[rank + c + half] = from_f32<AT>(v * cs + u * sn);
+            sn *= magnitude, cs *= magnitude;
+            const int a = rank + (interleaved ? 2 * c : c), b = rank + (interleaved ? 2 * c + 1 : c + half);
+            const float u = to_f32(src[a]), v = to_f32(src[b]);
+            dst[a] = from_f32<AT>(u * cs - v * sn);
+            dst[b] = from_f32<AT>(v * cs + u * sn);
         } else {
             dst[rank + c + half] = src[rank + c + half];
         }
@@ -341,16 +347,18 @@ __global__ void latent_store_kernel(const AT* __restrict__ rows, long long ld, c
 
 SHISO_API int shiso_latent_store(const void* rows, long long ld, int act_dtype, const float* w, const float* inv_freq,
                                  const int* positions, const int* seq_of_token, const int* block_table, int table_width, void* cache,
-                                 int tokens, int rank, int width, int rotary_dim, int page_size, float eps, cudaStream_t stream) {
+                                 int tokens, int rank, int width, int rotary_dim, int page_size, float eps, float magnitude,
+                                 int interleaved, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (rank <= 0 || width < rank || rotary_dim % 2 || rotary_dim > width - rank) return SHISO_ERR_SHAPE;
     const int threads = rank >= 512 ? 256 : 128;
     if (act_dtype == SHISO_F32)
         launch_kernel(latent_store_kernel<float>, tokens, threads, 0, stream, (const float*)rows, ld, w, inv_freq, positions,
-                      seq_of_token, block_table, table_width, (float*)cache, rank, width, rotary_dim, page_size, eps);
+                      seq_of_token, block_table, table_width, (float*)cache, rank, width, rotary_dim, page_size, eps, magnitude, interleaved);
     else if (act_dtype == SHISO_BF16)
         launch_kernel(latent_store_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)rows, ld, w, inv_freq,
-                      positions, seq_of_token, block_table, table_width, (__nv_bfloat16*)cache, rank, width, rotary_dim, page_size, eps);
+                      positions, seq_of_token, block_table, table_width, (__nv_bfloat16*)cache, rank, width, rotary_dim, page_size, eps, magnitude,
+                      interleaved);
     else
         return SHISO_ERR_DTYPE;
     return launch_status();

@@ -1,0 +1,211 @@
+// Row kernels of a residual stream whose norm has no statistics, and of attention heads that are
+// normalised together.
+//
+// add_dyt_kernel:      x = residual (+ up to two block outputs), stored back; out = tanh(alpha x) * w + b.
+// stream_add_kernel:   out = residual + up to three blocks of rows (each float or bfloat16) + one vector
+//                      that is the same for every row; out may be the residual itself.
+// glu_act_kernel:      the gated pair of a feed-forward over rows [gate | up]: silu(g) u, the tanh form
+//                      of gelu(g) u, or min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1).
+// joined_norm_store:   rows [q | k | (v) | ..]: one RMS norm over all query columns together and one
+//                      over all key columns, each with a weight per column; the queries times a
+//                      temperature 1 + coef * ln(floor((p + 1) / every) + 1) of the row's position p,
+//                      written back in place; normed keys to the paged key cache; to the value cache
+//                      the value columns, or (values_from_keys) the key columns as they came.
+//
+// Everything is evaluated in float with the library's tanhf, expf and logf, whatever the row type.
+#include "common.cuh"
+
+enum { GLU_SILU = 0, GLU_GELU_TANH = 1, GLU_SWISH_CLAMPED = 2 };
+
+__device__ __forceinline__ float glu_pair(float g, float u, int act, float limit) {
+    if (act == GLU_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (act == GLU_SWISH_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
+__device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i) {
+    return dtype == SHISO_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+// --------------------------------------------------------------------------- tanh norm
+
+// One thread per four neighbouring columns of a row (VEC) or per column.
+template <typename AT, bool VEC>
+__global__ void __launch_bounds__(256)
+add_dyt_kernel(float* __restrict__ residual, const AT* __restrict__ d0, const AT* __restrict__ d1, const int* __restrict__ rows,
+               const float* __restrict__ w, const float* __restrict__ b, float alpha, AT* __restrict__ out, int out_rows, int hidden) {
+    pdl_begin();
+    constexpr int N = VEC ? 4 : 1;
+    const int per_row = hidden / N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)out_rows * per_row) return;
+    const int r = (int)(i / per_row), c = (int)(i % per_row) * N;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden + c;
+    float x[N];
+    if constexpr (VEC) {
+        const float4 v = *reinterpret_cast<const float4*>(residual + src);
+        x[0] = v.x, x[1] = v.y, x[2] = v.z, x[3] = v.w;
+    } else {
+        x[0] = residual[src];
+    }
+    if (d0) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) x[e] += to_f32(d0[src + e]);
+    }
+    if (d1) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) x[e] += to_f32(d1[src + e]);
+    }
+    if (!rows && (d0 || d1)) {
+        if constexpr (VEC) *reinterpret_cast<float4*>(residual + src) = make_float4(x[0], x[1], x[2], x[3]);
+        else residual[src] = x[0];
+    }
+    AT* dst = out + (size_t)r * hidden + c;
+#pragma unroll
+    for (int e = 0; e < N; ++e) dst[e] = from_f32<AT>(tanhf(alpha * x[e]) * w[c + e] + b[c + e]);
+}
+
+// residual float [T, hidden]; d0, d1: block outputs in the output type, or null; rows: the rows
+// wanted (the residual is then left alone), or null for all of them (the sum is stored back).
+SHISO_API int shiso_add_dyt(float* residual, const void* d0, const void* d1, const int* rows, const float* w, const float* b,
+                            float alpha, void* out, int out_dtype, int out_rows, int hidden, cudaStream_t stream) {
+    if (out_rows <= 0 || hidden <= 0) return SHISO_OK;
+    const bool vec = hidden % 4 == 0 && (((uintptr_t)residual) & 15) == 0;
+    const unsigned blocks = ceil_div_u((long long)out_rows * (hidden / (vec ? 4 : 1)), 256);
+#define DYT_GO(AT)                                                                                                              \
+    {                                                                                                                           \
+        if (vec) launch_kernel(add_dyt_kernel<AT, true>, blocks, 256, 0, stream, residual, (const AT*)d0, (const AT*)d1, rows, w, b, alpha, (AT*)out, out_rows, hidden); \
+        else launch_kernel(add_dyt_kernel<AT, false>, blocks, 256, 0, stream, residual, (const AT*)d0, (const AT*)d1, rows, w, b, alpha, (AT*)out, out_rows, hidden);   \
+        return launch_status();                                                                                                 \
+    }
+    if (out_dtype == SHISO_F32) DYT_GO(float)
+    if (out_dtype == SHISO_BF16) DYT_GO(__nv_bfloat16)
+#undef DYT_GO
+    return SHISO_ERR_DTYPE;
+}
+
+// --------------------------------------------------------------------------- rows added to the stream
+
+struct StreamAddArgs {
+    const float* residual;
+    float* out;
+    const void* d[3];
+    int dtype[3];
+    const float* vector;  // [hidden] or null
+    long long total;
+    int hidden;
+};
+
+__global__ void __launch_bounds__(256) stream_add_kernel(const StreamAddArgs a) {
+    pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.total) return;
+    float x = a.residual[i];
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+        if (a.d[j]) x += load_as_f32(a.d[j], a.dtype[j], (size_t)i);
+    if (a.vector) x += a.vector[i % a.hidden];
+    a.out[i] = x;
+}
+
+SHISO_API int shiso_stream_add(const float* residual, float* out, const void* d0, int d0_dtype, const void* d1, int d1_dtype,
+                               const void* d2, int d2_dtype, const float* vector, int tokens, int hidden, cudaStream_t stream) {
+    if (tokens <= 0 || hidden <= 0) return SHISO_OK;
+    StreamAddArgs a = {residual, out, {d0, d1, d2}, {d0_dtype, d1_dtype, d2_dtype}, vector, (long long)tokens * hidden, hidden};
+    for (int j = 0; j < 3; ++j)
+        if (a.d[j] && a.dtype[j] != SHISO_F32 && a.dtype[j] != SHISO_BF16) return SHISO_ERR_DTYPE;
+    launch_kernel(stream_add_kernel, ceil_div_u(a.total, 256), 256, 0, stream, a);
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------- gated pairs
+
+template <typename AT>
+__global__ void __launch_bounds__(256)
+glu_act_kernel(const AT* __restrict__ gate_up, AT* __restrict__ out, int inter, long long total, int act, float limit) {
+    pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / inter;
+    const int c = (int)(i % inter);
+    const AT* row = gate_up + (size_t)t * 2 * inter;
+    out[i] = from_f32<AT>(glu_pair(to_f32(row[c]), to_f32(row[inter + c]), act, limit));
+}
+
+SHISO_API int shiso_glu_act(const void* gate_up, void* out, int act_dtype, int tokens, int inter, int act, float limit,
+                            cudaStream_t stream) {
+    if (tokens <= 0 || inter <= 0) return SHISO_OK;
+    if (act < GLU_SILU || act > GLU_SWISH_CLAMPED) return SHISO_ERR_SHAPE;
+    const long long total = (long long)tokens * inter;
+    const unsigned blocks = ceil_div_u(total, 256);
+    if (act_dtype == SHISO_F32)
+        launch_kernel(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total, act, limit);
+    else if (act_dtype == SHISO_BF16)
+        launch_kernel(glu_act_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter,
+                      total, act, limit);
+    else
+        return SHISO_ERR_DTYPE;
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------- heads normalised together
+
+// One block per row.  Columns [0, q_cols) are the queries, [q_cols, q_cols + k_cols) the keys,
+// v_cols columns from v_col on the values (v_col = q_cols when the values are the keys as they came).
+template <typename AT>
+__global__ void __launch_bounds__(256)
+joined_norm_store_kernel(AT* __restrict__ proj, long long ld, int q_cols, int k_cols, int v_col, int v_cols, const float* __restrict__ q_w,
+                         const float* __restrict__ k_w, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                         const int* __restrict__ table, int table_width, AT* __restrict__ k_cache, AT* __restrict__ v_cache,
+                         int page_size, float eps, float temp_coef, int temp_every) {
+    pdl_begin();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    AT* row = proj + (size_t)t * ld;
+    const int pos = positions[t];
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) {
+        const float v = to_f32(row[i]);
+        sq += v * v;
+    }
+    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
+        const float v = to_f32(row[q_cols + i]);
+        sk += v * v;
+    }
+    float q_inv = rsqrtf(block_sum(sq, scratch) / (float)q_cols + eps);
+    const float k_inv = rsqrtf(block_sum(sk, scratch) / (float)k_cols + eps);
+    if (temp_every > 0) q_inv *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+    const int page = table[(size_t)seq_of_token[t] * table_width + pos / page_size];
+    if (page >= 0) {
+        const size_t at = (size_t)page * page_size + pos % page_size;
+        AT* k_dst = k_cache + at * k_cols;
+        AT* v_dst = v_cache + at * v_cols;
+        for (int i = threadIdx.x; i < k_cols; i += blockDim.x) k_dst[i] = from_f32<AT>(to_f32(row[q_cols + i]) * k_inv * k_w[i]);
+        for (int i = threadIdx.x; i < v_cols; i += blockDim.x) v_dst[i] = row[v_col + i];
+    }
+    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) row[i] = from_f32<AT>(to_f32(row[i]) * q_inv * q_w[i]);
+}
+
+SHISO_API int shiso_joined_norm_store(void* proj, long long ld, int act_dtype, int q_cols, int k_cols, int v_col, int v_cols,
+                                      const float* q_w, const float* k_w, const int* positions, const int* seq_of_token,
+                                      const int* table, int table_width, void* k_cache, void* v_cache, int tokens, int page_size,
+                                      float eps, float temp_coef, int temp_every, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (q_cols <= 0 || k_cols <= 0 || v_cols <= 0 || v_col < q_cols || page_size <= 0 || temp_every < 0) return SHISO_ERR_SHAPE;
+    const int threads = q_cols >= 1024 ? 256 : 128;
+    if (act_dtype == SHISO_F32)
+        launch_kernel(joined_norm_store_kernel<float>, tokens, threads, 0, stream, (float*)proj, ld, q_cols, k_cols, v_col, v_cols, q_w,
+                      k_w, positions, seq_of_token, table, table_width, (float*)k_cache, (float*)v_cache, page_size, eps, temp_coef,
+                      temp_every);
+    else if (act_dtype == SHISO_BF16)
+        launch_kernel(joined_norm_store_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (__nv_bfloat16*)proj, ld, q_cols, k_cols,
+                      v_col, v_cols, q_w, k_w, positions, seq_of_token, table, table_width, (__nv_bfloat16*)k_cache,
+                      (__nv_bfloat16*)v_cache, page_size, eps, temp_coef, temp_every);
+    else
+        return SHISO_ERR_DTYPE;
+    return launch_status();
+}

@@ -74,22 +74,27 @@ _SIGNATURES = {
     "shiso_add_layernorm": [P, P, P, P, P, P, I, I, I, F, P],
     "shiso_group_rmsnorm": [P, I, LL, P, LL, P, P, I, I, I, I, I, F, P],
     "shiso_causal_conv": [P, LL, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
-    "shiso_rotate_heads": [P, LL, LL, P, LL, LL, I, P, P, I, I, I, I, P],
-    "shiso_latent_store": [P, LL, I, P, P, P, P, P, I, P, I, I, I, I, I, F, P],
+    "shiso_rotate_heads": [P, LL, LL, P, LL, LL, I, P, P, I, I, I, I, F, I, P],
+    "shiso_latent_store": [P, LL, I, P, P, P, P, P, I, P, I, I, I, I, I, F, F, I, P],
     "shiso_state_recurrence": [P, P, P, P, LL, LL, LL, LL, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P],
     "shiso_head_linear": [P, LL, LL, I, P, I, P, LL, LL, I, P, LL, I, I, I, I, P],
-    "shiso_moe_route": [P, P, P, I, I, I, I, I, F, I, I, P],
-    "shiso_routed_experts": [P, I, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
+    "shiso_moe_route": [P, LL, P, P, P, I, I, I, I, I, F, I, I, F, P],
+    "shiso_routed_experts": [P, I, P, P, P, P, I, P, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "shiso_latent_attention_smem": [I, I],
     "shiso_latent_attention": [P, I, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
     "shiso_latent_prefill_supported": [I, I],
     "shiso_latent_prefill": [P, P, P, I, P, P, P, I, I, I, I, I, I, F, P],
     "shiso_head_prepare_store": [P, LL, I, I, I, I, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, I, P],
-    "shiso_masked_attention": [P, LL, I, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, F, F, I, I, I, I, I, P, P],
+    "shiso_masked_attention": [P, LL, I, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, F, F, I, I, I, I, I, P, I, P],
     "shiso_masked_attention_tiles_supported": [I, I],
-    "shiso_masked_attention_tiles": [P, LL, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, I, F, F, I, I, I, I, P],
+    "shiso_masked_attention_tiles": [P, LL, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, I, F, F, I, I, I, I, I, P],
     "shiso_norm_into": [P, P, I, P, P, I, I, F, P],
     "shiso_polynorm": [P, LL, I, P, P, I, I, F, P],
+    "shiso_embed_scaled": [P, P, P, P, I, P, I, I, I, F, P],
+    "shiso_add_dyt": [P, P, P, P, P, P, F, P, I, I, I, P],
+    "shiso_stream_add": [P, P, P, I, P, I, P, I, P, I, I, P],
+    "shiso_glu_act": [P, P, I, I, I, I, F, P],
+    "shiso_joined_norm_store": [P, LL, I, I, I, I, I, P, P, P, P, P, I, P, P, I, I, F, F, I, P],
 }
 
 

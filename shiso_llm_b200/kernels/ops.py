@@ -172,10 +172,10 @@ def _done(status: int, what: str, launches: int = 1, shape=()) -> None:
 # --------------------------------------------------------------------------- rows
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=None) -> torch.Tensor:
-    """Rows of ``table`` for ``ids``.  Where ``feed_index[t] >= 0`` the id is read on the device
-    from ``fed_tokens[feed_index[t]]`` instead (a token picked a step earlier that the host has
-    not seen)."""
+def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=None, scale: float = 1.0) -> torch.Tensor:
+    """Rows of ``table`` for ``ids``, times ``scale`` (in float32).  Where ``feed_index[t] >= 0`` the
+    id is read on the device from ``fed_tokens[feed_index[t]]`` instead (a token picked a step
+    earlier that the host has not seen)."""
     _check(ids, "ids", torch.int32, 1)
     _check(table, "embedding table", None, 2)
     tokens, (vocab, hidden) = ids.shape[0], table.shape
@@ -187,10 +187,67 @@ def embed(ids: torch.Tensor, table: torch.Tensor, feed_index=None, fed_tokens=No
         if feed_index.shape[0] != tokens:
             raise KernelError(f"feed_index has {feed_index.shape[0]} entries for {tokens} rows")
     out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
-    status = library().shiso_embed(
-        _ptr(ids), _ptr(feed_index), _ptr(fed_tokens), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, _stream()
+    status = library().shiso_embed_scaled(
+        _ptr(ids), _ptr(feed_index), _ptr(fed_tokens), _ptr(table), _code(table), _ptr(out), tokens, hidden, vocab, float(scale), _stream()
     )
     _done(status, "embed", shape=(tokens, hidden))
+    return out
+
+
+def stream_add(residual, deltas, vector, in_place=True):
+    """``residual + sum(deltas) + vector``: float32 rows ``[T, H]``, up to three blocks of rows of the
+    same shape (float32 or bfloat16 each) and a float32 vector ``[H]`` added to every row (or None).
+    Written into ``residual``, or with ``in_place=False`` into rows of their own; returns them."""
+    _check(residual, "residual", torch.float32, 2)
+    tokens, hidden = residual.shape
+    deltas = tuple(deltas)
+    if len(deltas) > 3:
+        raise KernelError(f"{len(deltas)} blocks of rows to add; the kernel takes three")
+    for d in deltas:
+        _check(d, "rows to add", None, 2)
+        if d.shape != residual.shape:
+            raise KernelError(f"rows of {tuple(d.shape)} added to a residual of {tuple(residual.shape)}")
+    if vector is not None:
+        _check(vector, "vector", torch.float32, 1)
+        if vector.shape[0] != hidden:
+            raise KernelError(f"a vector of {vector.shape[0]} for rows of {hidden}")
+    out = residual if in_place else torch.empty_like(residual)
+    d = list(deltas) + [None] * (3 - len(deltas))
+    status = library().shiso_stream_add(
+        _ptr(residual), _ptr(out), _ptr(d[0]), _code(d[0]) if d[0] is not None else 0, _ptr(d[1]), _code(d[1]) if d[1] is not None else 0,
+        _ptr(d[2]), _code(d[2]) if d[2] is not None else 0, _ptr(vector), tokens, hidden, _stream(),
+    )
+    _done(status, "stream_add", shape=(tokens, hidden))
+    return out
+
+
+def add_dyt(residual, deltas, alpha, w, b, out_dtype, rows=None):
+    """``tanh(alpha * x) * w + b`` of ``x = residual + sum(deltas)``: ``residual`` float32 ``[T, H]``,
+    up to two ``deltas`` ``[T, H]`` in the output type.  Without ``rows`` the sum is stored back into
+    ``residual``; with ``rows`` (int32) only those rows are summed and squashed, into ``[len(rows), H]``."""
+    _check(residual, "residual", torch.float32, 2)
+    _check(w, "norm weight", torch.float32, 1)
+    _check(b, "norm bias", torch.float32, 1)
+    tokens, hidden = residual.shape
+    if w.shape[0] != hidden or b.shape[0] != hidden:
+        raise KernelError(f"norm weight / bias of {w.shape[0]} / {b.shape[0]} entries for rows of {hidden}")
+    deltas = tuple(deltas)
+    if len(deltas) > 2:
+        raise KernelError(f"{len(deltas)} block outputs to add; the kernel takes two")
+    for d in deltas:
+        _check(d, "delta", out_dtype, 2)
+        if d.shape != residual.shape:
+            raise KernelError(f"delta {tuple(d.shape)} does not match the residual {tuple(residual.shape)}")
+    out_rows = tokens
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        out_rows = rows.shape[0]
+    out = torch.empty((out_rows, hidden), dtype=out_dtype, device=residual.device)
+    d = list(deltas) + [None] * (2 - len(deltas))
+    status = library().shiso_add_dyt(
+        _ptr(residual), _ptr(d[0]), _ptr(d[1]), _ptr(rows), _ptr(w), _ptr(b), float(alpha), _ptr(out), _code(out), out_rows, hidden, _stream()
+    )
+    _done(status, "dyt" if not deltas else "add + dyt", shape=(out_rows, hidden))
     return out
 
 
@@ -365,6 +422,34 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype
         _done(status, "linear_swiglu (tcgen05)", shape=(tokens, two_inter, k))
         return out
     return swiglu(linear(x, gate_up, out_dtype))
+
+
+_GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
+
+
+def glu_act(gate_up: torch.Tensor, act: str, limit: float = 0.0) -> torch.Tensor:
+    """The gated pair over rows ``[gate | up]``: "silu" ``silu(g) u``; "gelu_tanh" ``gelu(g) u`` in
+    its tanh form; "swish_clamped" ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(g, limit)`` and
+    ``u' = clamp(u, -limit, limit)``.  Evaluated in float32."""
+    _check(gate_up, "gate_up", None, 2)
+    if act not in _GLU_ACTS:
+        raise KernelError(f"gated pair {act!r}: expected one of {sorted(_GLU_ACTS)}")
+    tokens, two_inter = gate_up.shape
+    if two_inter % 2:
+        raise KernelError(f"gate_up rows of {two_inter} cannot be split in two halves")
+    out = torch.empty((tokens, two_inter // 2), dtype=gate_up.dtype, device=gate_up.device)
+    status = library().shiso_glu_act(_ptr(gate_up), _ptr(out), _code(gate_up), tokens, two_inter // 2, _GLU_ACTS[act], float(limit), _stream())
+    _done(status, f"glu_act ({act})", shape=(tokens, two_inter // 2))
+    return out
+
+
+def linear_glu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype, act: str, limit: float = 0.0) -> torch.Tensor:
+    """``act(x @ gate^T, x @ up^T)`` for ``gate_up = [gate; up]`` (the pairs of ``glu_act``).  The
+    silu pair takes ``linear_swiglu`` and its epilogues; the others run the product and then the
+    activation kernel."""
+    if act == "silu":
+        return linear_swiglu(x, gate_up, out_dtype)
+    return glu_act(linear(x, gate_up, out_dtype), act, limit)
 
 
 STREAM_MAX_TOKENS = 8  # rows for which the weight-streaming kernel runs the product-into-stream / scaled-product pair
@@ -1182,14 +1267,49 @@ def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_ord
     return proj[:, :q_cols]
 
 
+def joined_norm_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, q_temperature, values_from_keys, step, k_cache, v_cache,
+                      block_table, page_size):
+    """Prepares ``proj[T, heads*dim | kv_heads*dim | (kv_heads*vdim) | ...]`` in place: ONE RMS norm over
+    all query columns together (weight ``q_w[heads*dim]``) and one over all key columns
+    (``k_w[kv_heads*dim]``); the queries times ``1 + coef * ln(floor((p + 1) / every) + 1)`` at
+    position ``p`` when ``q_temperature = (coef, every)``.  Queries are written back where they
+    stood, normed keys go to the paged key cache, and the value cache gets the value columns or,
+    with ``values_from_keys``, the key columns as they came.  Returns the query columns."""
+    act = proj.dtype
+    q_cols, k_cols, v_cols = heads * dim, kv_heads * dim, kv_heads * vdim
+    ld = _rows(proj, "projected rows", act)
+    if values_from_keys and vdim != dim:
+        raise KernelError(f"values that are the keys have their size {dim}, not {vdim}")
+    if proj.shape[1] < q_cols + k_cols + (0 if values_from_keys else v_cols):
+        raise KernelError(f"projected rows of {proj.shape[1]} do not hold {heads} + {kv_heads} heads of {dim}")
+    _check(q_w, "q norm weight", torch.float32, 1)
+    _check(k_w, "k norm weight", torch.float32, 1)
+    if q_w.shape[0] != q_cols or k_w.shape[0] != k_cols:
+        raise KernelError(f"norm weights of {q_w.shape[0]} / {k_w.shape[0]} entries for {q_cols} query and {k_cols} key columns")
+    _check(block_table, "block table", torch.int32, 2)
+    _paged(k_cache, "k cache", act, page_size)
+    _paged(v_cache, "v cache", act, page_size)
+    if k_cache.shape[2:] != (kv_heads, dim) or v_cache.shape[2:] != (kv_heads, vdim):
+        raise KernelError(f"caches of shape {tuple(k_cache.shape)} / {tuple(v_cache.shape)} for {kv_heads} heads of {dim} / {vdim}")
+    coef, every = q_temperature if q_temperature is not None else (0.0, 0)
+    status = library().shiso_joined_norm_store(
+        proj.data_ptr(), ld, _CODES[act], q_cols, k_cols, q_cols if values_from_keys else q_cols + k_cols, v_cols, _ptr(q_w), _ptr(k_w),
+        _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_cache), _ptr(v_cache),
+        proj.shape[0], page_size, float(eps), float(coef), int(every), _stream(),
+    )
+    _done(status, "joined_norm_store", shape=(proj.shape[0], heads + kv_heads, dim))
+    return proj[:, :q_cols]
+
+
 def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, mask, size, keep_first, step, *, sigmoid=False,
-                     key_bias=None, softcap=None, gate=None, general=False):
+                     key_bias=None, softcap=None, gate=None, general=False, gate_per_element=False):
     """Attention of every row over the keys its mask shows: ``mask`` "window" (the last ``size``
     positions and the first ``keep_first`` of the sequence) or "chunk" (the positions of the row's
     own run of ``size``, counted from 0).  Scores ``(q . k) * scale``, capped as
     ``softcap * tanh(score / softcap)`` when a cap is given; weights a softmax, or with ``sigmoid``
     one ``sigmoid(score + key_bias[head])`` per key, not normalised.  ``gate[T, heads]`` (logits)
-    multiplies each head's output by its sigmoid.  ``q`` and ``gate`` may be column ranges.
+    multiplies each head's output by its sigmoid; with ``gate_per_element`` it is ``[T, heads * vdim]``
+    and every output entry has a gate of its own.  ``q`` and ``gate`` may be column ranges.
     Returns ``[T, heads * vdim]``.  bfloat16 steps that hold prompt portions take the tiled
     tensor-core kernel (key sizes in multiples of 16 up to 256, value sizes up to 128); steps of
     single tokens, float32 and other sizes take the general kernel, as does ``general=True``
@@ -1206,7 +1326,8 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
         _check(key_bias, "key bias", torch.float32, 1)
         if key_bias.shape[0] != heads:
             raise KernelError(f"key bias has {key_bias.shape[0]} entries for {heads} heads")
-    gate_ld = _rows(gate, "gate", act, heads) if gate is not None else 0
+    gate_ld = _rows(gate, "gate", act, heads * (vdim if gate_per_element else 1)) if gate is not None else 0
+    wide = int(bool(gate is not None and gate_per_element))
     tokens = q.shape[0]
     out = torch.empty((tokens, heads * vdim), dtype=act, device=q.device)
     lib = library()
@@ -1260,7 +1381,7 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
             q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
             _ptr(step.start_pos), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
             step.num_seqs, tiles, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size),
-            int(keep_first), int(bool(sigmoid)), _stream(),
+            int(keep_first), int(bool(sigmoid)), wide, _stream(),
         )
         _done(status, f"masked_attention_tiles {what}", shape=(tokens, heads, dim))
         return out
@@ -1274,7 +1395,7 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
         q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
         _ptr(step.seq_of_token), _ptr(out), heads * vdim, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(key_bias),
         tokens, heads, kv_heads, dim, vdim, page_size, float(scale), float(softcap or 0.0), _MASKS[mask], int(size), int(keep_first),
-        int(bool(sigmoid)), splits, _ptr(scratch), _stream(),
+        int(bool(sigmoid)), splits, _ptr(scratch), wide, _stream(),
     )
     _done(status, f"masked_attention {what}", 2 if splits > 1 else 1, shape=(tokens, heads, dim))
     return out
@@ -1452,10 +1573,11 @@ def _heads3(t, name, dtype):
     return t.stride(0), t.stride(1)
 
 
-def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size):
+def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size, magnitude=1.0, interleaved=False):
     """Each row ``[latent (rank) | shared key part]`` (a column range may be given): the latent
     RMS-normed with ``norm_w``, the rest rotated by the row's position (half-split pairs over
-    ``rotary_dim``); stored as the position's row of ``k_cache [pages, page_size, 1, width]``."""
+    ``rotary_dim``, or neighbours with ``interleaved``; cosine and sine times ``magnitude``); stored
+    as the position's row of ``k_cache [pages, page_size, 1, width]``."""
     tokens, width = rows.shape
     ld = _rows(rows, "rows", k_cache.dtype, width)
     _paged(k_cache, "latent cache", rows.dtype, page_size)
@@ -1472,14 +1594,15 @@ def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, b
     status = library().shiso_latent_store(
         rows.data_ptr(), ld, _code(rows), _ptr(norm_w), _ptr(inv_freq) if rotary_dim else 0, _ptr(step.positions),
         _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_cache), tokens, int(rank), width, int(rotary_dim),
-        page_size, float(eps), _stream(),
+        page_size, float(eps), float(magnitude), int(bool(interleaved)), _stream(),
     )
     _done(status, "latent_store", shape=(tokens, width))
 
 
-def rotate_heads(x, out, inv_freq, rotary_dim, step):
-    """``x[T, H, W]`` with the half-split pairs of its first ``rotary_dim`` columns turned by each row's
-    position, into ``out[T, H, W]``; both may be column ranges of wider rows."""
+def rotate_heads(x, out, inv_freq, rotary_dim, step, magnitude=1.0, interleaved=False):
+    """``x[T, H, W]`` with the half-split pairs (neighbours with ``interleaved``) of its first
+    ``rotary_dim`` columns turned by each row's position, cosine and sine times ``magnitude``, into
+    ``out[T, H, W]``; both may be column ranges of wider rows."""
     act = x.dtype
     x_ld, x_hs = _heads3(x, "x", act)
     out_ld, out_hs = _heads3(out, "out", act)
@@ -1492,7 +1615,7 @@ def rotate_heads(x, out, inv_freq, rotary_dim, step):
     tokens, heads, width = x.shape
     status = library().shiso_rotate_heads(
         x.data_ptr(), x_ld, x_hs, out.data_ptr(), out_ld, out_hs, _CODES[act], _ptr(inv_freq) if rotary_dim else 0,
-        _ptr(step.positions), tokens, heads, width, int(rotary_dim), _stream(),
+        _ptr(step.positions), tokens, heads, width, int(rotary_dim), float(magnitude), int(bool(interleaved)), _stream(),
     )
     _done(status, "rotate_heads", shape=(tokens, heads, width))
 
@@ -1571,29 +1694,39 @@ def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step, 
 # --------------------------------------------------------------------------- mixture of experts
 
 
-def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False):
-    """For every row of ``logits`` (float32 ``[T, E]``): scores (softmax over all experts, or
-    sigmoids), the ``top`` largest among the experts of the ``group_keep`` best of ``group_count``
-    groups of neighbours (a group's score is its largest), and their weights: the scores (divided
-    by their sum with ``renormalize``) times ``scale``.  Returns ids int32 and weights float32,
-    both ``[T, top]``, best first."""
-    _check(logits, "router logits", torch.float32, 2)
+def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False, correction=None, renorm_eps=0.0):
+    """For every row of ``logits`` (float32 ``[T, E]``, a column range may be given): scores (softmax
+    over all experts, or sigmoids), the ``top`` largest among the experts of the ``group_keep`` best
+    of ``group_count`` groups of neighbours (a group's value is its largest), ranked by score +
+    ``correction[e]`` where a correction (float32 ``[E]``) is given, and their weights: the scores
+    themselves (divided by their sum + ``renorm_eps`` with ``renormalize``) times ``scale``.  Returns
+    ids int32 and weights float32, both ``[T, top]``, best first."""
+    ld = _rows(logits, "router logits", torch.float32)
     tokens, experts = logits.shape
+    if correction is not None:
+        _check(correction, "router correction", torch.float32, 1)
+        if correction.shape[0] != experts:
+            raise KernelError(f"a correction of {correction.shape[0]} entries for {experts} experts")
     ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     status = library().shiso_moe_route(
-        _ptr(logits), _ptr(ids), _ptr(weights), tokens, experts, int(top), int(group_count), int(group_keep), float(scale),
-        int(bool(sigmoid)), int(bool(renormalize)), _stream(),
+        logits.data_ptr(), ld, _ptr(correction), _ptr(ids), _ptr(weights), tokens, experts, int(top), int(group_count), int(group_keep),
+        float(scale), int(bool(sigmoid)), int(bool(renormalize)), float(renorm_eps), _stream(),
     )
     _done(status, "moe_route", shape=(tokens, experts, top))
     return ids, weights
 
 
-def routed_experts(x, ids, weights, gate_up, down, extra=None):
+MOE_MAX_EXPERTS = 256  # router outputs the grouping kernels keep in shared memory
+
+
+def routed_experts(x, ids, weights, gate_up, down, extra=None, act="silu", limit=0.0, extra_gate=None, identity=0):
     """``out[t] = extra[t] + sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` with gated experts
-    ``down[e] (silu(gate x) * (up x))``, ``gate_up[e] = [gate; up]``: ``x[T, H]``, ``gate_up[E, 2F, H]``,
-    ``down[E, H, F]``.  The (row, choice) pairs are grouped by expert on the device; nothing about the
-    routing reaches the host."""
+    ``down[e] pair(gate x, up x)`` (``act`` / ``limit``: the pairs of ``glu_act``), ``gate_up[e] =
+    [gate; up]``: ``x[T, H]``, ``gate_up[E, 2F, H]``, ``down[E, H, F]``.  Ids ``E .. E + identity - 1`` are
+    identity experts: one adds ``weights[t, j] * x[t]``.  ``extra_gate`` (float32 ``[T, 1]``, a column
+    range may be given) multiplies ``extra[t]`` by its sigmoid.  The (row, choice) pairs are grouped
+    by expert on the device; nothing about the routing reaches the host."""
     _check(x, "x", None, 2)
     _check(ids, "expert ids", torch.int32, 2)
     _check(weights, "expert weights", torch.float32, 2)
@@ -1608,14 +1741,26 @@ def routed_experts(x, ids, weights, gate_up, down, extra=None):
         _check(extra, "extra", x.dtype, 2)
         if extra.shape != x.shape:
             raise KernelError(f"extra rows of {tuple(extra.shape)} beside {tuple(x.shape)}")
+    if act not in _GLU_ACTS:
+        raise KernelError(f"gated pair {act!r}: expected one of {sorted(_GLU_ACTS)}")
+    gate_ld = 0
+    if extra_gate is not None:
+        if extra is None:
+            raise KernelError("a gate on extra rows that are absent")
+        gate_ld = _rows(extra_gate, "extra gate", torch.float32, 1)
+        if extra_gate.shape[0] != tokens:
+            raise KernelError(f"{extra_gate.shape[0]} gates for {tokens} rows")
     ff, total = two_ff // 2, tokens * top
-    ints = torch.empty((experts + 3 * total,), dtype=torch.int32, device=x.device)
+    if identity < 0 or experts + identity > MOE_MAX_EXPERTS:
+        raise KernelError(f"{experts} experts and {identity} identity experts; the grouping kernels take {MOE_MAX_EXPERTS} in all")
+    ints = torch.empty((experts + identity + 3 * total,), dtype=torch.int32, device=x.device)
     mid = torch.empty((total, ff), dtype=x.dtype, device=x.device)
     y = torch.empty((total, hidden), dtype=torch.float32, device=x.device)
     out = torch.empty_like(x)
     status = library().shiso_routed_experts(
-        _ptr(x), _code(x), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down), _code(gate_up), _ptr(extra), _ptr(out), _ptr(ints),
-        _ptr(mid), _ptr(y), tokens, hidden, ff, experts, top, _stream(),
+        _ptr(x), _code(x), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down), _code(gate_up), _ptr(extra),
+        extra_gate.data_ptr() if extra_gate is not None else 0, gate_ld, _ptr(out), _ptr(ints),
+        _ptr(mid), _ptr(y), tokens, hidden, ff, experts, int(identity), top, _GLU_ACTS[act], float(limit), _stream(),
     )
     _done(status, "routed_experts", 6, shape=(tokens, top, experts, ff, hidden))
     return out

@@ -240,5 +240,6 @@ class RoutedExperts(FeedForward):
             more["act"], more["limit"] = self.activation, self.limit
         if self.shared_gate_name is not None:
             more["extra_gate"] = logits[:, self.experts :]  # [T, 1] float32 logits
-        # ids from the matrices' count on are identity experts (the routed_experts op sees it from the stacks)
+        if self.identity:
+            more["identity"] = self.identity
         return ops.routed_experts(x, ids, weights, self.gate_up, self.down, extra, **more)

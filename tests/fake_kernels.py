@@ -677,7 +677,7 @@ def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renorm
     return ids.to(torch.int32), (w * scale).to(torch.float32)
 
 
-def routed_experts(x, ids, weights, gate_up, down, extra=None, act="silu", limit=0.0, extra_gate=None):
+def routed_experts(x, ids, weights, gate_up, down, extra=None, act="silu", limit=0.0, extra_gate=None, identity=0):
     """``sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` (+ ``extra``, times ``sigmoid(extra_gate[t])``
     where one is given), in ``x``'s type.  An id from the number of stacked matrices on is an
     identity expert: its output is ``x[t]``."""
@@ -693,6 +693,7 @@ def routed_experts(x, ids, weights, gate_up, down, extra=None, act="silu", limit
         for j in range(ids.shape[1]):
             e = int(ids[t, j])
             if e >= gate_up.shape[0]:
+                assert e < gate_up.shape[0] + identity, f"choice {e} beyond the experts and identity experts"
                 out[t] += float(weights[t, j]) * x64[t]
                 continue
             y = gate_up[e].to(F64) @ x64[t]
