@@ -66,7 +66,8 @@ def attention(tensors, prefix, m, h, eps):
     v = k  # as projected: the keys before their norm
     q = rms_norm(q, _w(tensors, f"{prefix}.q.norm"), eps)  # over all heads' entries together
     k = rms_norm(k, _w(tensors, f"{prefix}.k.norm"), eps)
-    q = q * query_temperature(positions, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None]
+    if m.get("q_temp") is not None:
+        q = q * query_temperature(positions, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None]
     q, k, v = q.view(T, H, D), k.view(T, G, D), v.view(T, G, V)
     out = torch.zeros((T, H, V), dtype=F64)
     for a in range(H):
