@@ -549,7 +549,9 @@ def test_feed_forwards_alone(backend, name):
             y = part.forward(h.to(env.device), None)
             y = (y.materialize() if hasattr(y, "materialize") else y).double().cpu()
             sure = torch.ones(rows, dtype=torch.bool) if not margins or dtype == torch.float32 else margins[0] > 0.02
-            close(y[sure], want[sure], dtype, f"{name} feed-forward, {rows} rows {dtype}", 4.0)
+            assert torch.isfinite(y).all()
+            if sure.any():  # (bfloat16: a row whose choice of experts hung on a close call may choose otherwise)
+                close(y[sure], want[sure], dtype, f"{name} feed-forward, {rows} rows {dtype}", 4.0)
 
 
 def test_the_clamped_pair_term_by_term():
