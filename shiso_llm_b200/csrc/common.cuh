@@ -78,6 +78,26 @@ __device__ __forceinline__ float silu_times(float g, float u) {
     return g * r * u;
 }
 
+// The gated pairs of a feed-forward in such an epilogue: silu(g) u; the tanh form of gelu, which is
+// g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)), times u; and the clamped pair
+// g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).  The same two
+// special-function instructions as silu_times.
+enum { SHISO_GLU_SILU = 0, SHISO_GLU_GELU_TANH = 1, SHISO_GLU_SWISH_CLAMPED = 2 };
+__device__ __forceinline__ float glu_times(float g, float u, int act, float limit) {
+    float z = g;  // the sigmoid's argument
+    if (act == SHISO_GLU_GELU_TANH) {
+        z = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+    } else if (act == SHISO_GLU_SWISH_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        z = 1.702f * g;
+    }
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r * u;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------
 // Every kernel is launched so that it may start while its predecessor in the stream is still
 // finishing.  It waits for the predecessor to complete and flush (griddepcontrol.wait) before

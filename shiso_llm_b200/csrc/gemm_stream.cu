@@ -102,6 +102,8 @@ struct StreamArgs {
     const float* bias;       // [N] or null (plain products only)
     void* y;                 // plain [T, N]; GLU [T, inter]
     int T, N, K, inter, out_f32, mode;
+    int glu_act;             // GLU: which gated pair (SHISO_GLU_*; 0: silu)
+    float glu_limit;         // its clamp
     int tiles;               // 16-row tiles (GLU: 8 gate + 8 up rows)
     int* status;
     // STREAM epilogue
@@ -498,7 +500,7 @@ gemm_stream_kernel(StreamArgs a) {
                 }
                 if (a.mode == MODE_GLU) {
                     if (rows[0] >= 0) {
-                        const float v = silu_times(lo, hi);
+                        const float v = glu_times(lo, hi, a.glu_act, a.glu_limit);
                         const size_t at = (size_t)token * a.inter + rows[0];
                         if (a.out_f32) ((float*)a.y)[at] = v;
                         else ((__nv_bfloat16*)a.y)[at] = __float2bfloat16_rn(v);
@@ -579,6 +581,28 @@ SHISO_API int shiso_gemm_stream(const void* x, const void* w, const float* bias,
     a.inter = inter;
     a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     a.mode = inter > 0 ? MODE_GLU : MODE_PLAIN;
+    return launch_stream(a, sm_count, stream);
+}
+
+// The gate/up pair with another gated pair than silu (SHISO_GLU_* of common.cuh): w [2 * inter, K], y [T, inter].
+SHISO_API int shiso_gemm_stream_glu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K, int act,
+                                    float limit, int sm_count, cudaStream_t stream) {
+    if (T <= 0 || inter <= 0) return SHISO_OK;
+    if (T > MAX_ROWS || K % 8 != 0 || K <= 0 || sm_count <= 0) return SHISO_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return SHISO_ERR_ALIGN;
+    if (act < SHISO_GLU_SILU || act > SHISO_GLU_SWISH_CLAMPED) return SHISO_ERR_SHAPE;
+    StreamArgs a = {};
+    a.x = (const __nv_bfloat16*)x;
+    a.w = (const __nv_bfloat16*)w;
+    a.y = y;
+    a.T = T;
+    a.N = 2 * inter;
+    a.K = K;
+    a.inter = inter;
+    a.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    a.mode = MODE_GLU;
+    a.glu_act = act;
+    a.glu_limit = limit;
     return launch_stream(a, sm_count, stream);
 }
 

@@ -53,6 +53,8 @@ struct GemmParams {
     int k_blocks_per_split;  // BK-blocks each CTA of a cluster handles
     int out_f32;             // 1: float output, 0: bfloat16
     int inter;               // GLU kernels: rows of the gate (and of the up) matrix, and of the output
+    int glu_act;             // GLU kernels: which gated pair (SHISO_GLU_*; 0: silu) ...
+    float glu_limit;         // ... and its clamp
     // SCALED (scale_partials != null): the rows of x lack their RMS scale; token t's is
     // rsqrt(sum over c < scale_count of scale_partials[c * scale_stride + t] / K + scale_eps) and
     // multiplies the accumulators of its column.
@@ -330,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             gate[j] *= sc;
                             up[j] *= sc;
                         }
-                        const float v = silu_times(gate[j], up[j]);
+                        const float v = glu_times(gate[j], up[j], p.glu_act, p.glu_limit);
                         const size_t at = (size_t)token * p.inter + feature;
                         if (p.out_f32) store_out<float>((float*)p.y, at, v);
                         else store_out<__nv_bfloat16>((__nv_bfloat16*)p.y, at, v);
@@ -470,8 +472,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
                 float4 v;
                 if (GLU) {
-                    v = make_float4(silu_times(sum[0].x, sum[A_TILES - 1].x), silu_times(sum[0].y, sum[A_TILES - 1].y),
-                                    silu_times(sum[0].z, sum[A_TILES - 1].z), silu_times(sum[0].w, sum[A_TILES - 1].w));
+                    v = make_float4(glu_times(sum[0].x, sum[A_TILES - 1].x, p.glu_act, p.glu_limit),
+                                    glu_times(sum[0].y, sum[A_TILES - 1].y, p.glu_act, p.glu_limit),
+                                    glu_times(sum[0].z, sum[A_TILES - 1].z, p.glu_act, p.glu_limit),
+                                    glu_times(sum[0].w, sum[A_TILES - 1].w, p.glu_act, p.glu_limit));
                 } else {
                     v = make_float4(sum[0].x + bias4.x, sum[0].y + bias4.y, sum[0].z + bias4.z, sum[0].w + bias4.w);
                 }
@@ -738,6 +742,21 @@ SHISO_API int shiso_gemm_tcgen05_swiglu(const void* x, const void* w, void* y, i
     p.y = y;
     p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     p.inter = inter;
+    return run_glu(p, x, w, stream);
+}
+
+// The same with another gated pair than silu (SHISO_GLU_* of common.cuh).
+SHISO_API int shiso_gemm_tcgen05_glu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K, int act,
+                                     float limit, cudaStream_t stream) {
+    if (T <= 0 || inter <= 0) return SHISO_OK;
+    if (!shiso_gemm_tcgen05_supported(K, x, w)) return SHISO_ERR_UNSUPPORTED;
+    if (act < SHISO_GLU_SILU || act > SHISO_GLU_SWISH_CLAMPED) return SHISO_ERR_SHAPE;
+    GemmParams p = blank_params(T, 2 * inter, K);
+    p.y = y;
+    p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
+    p.inter = inter;
+    p.glu_act = act;
+    p.glu_limit = limit;
     return run_glu(p, x, w, stream);
 }
 

@@ -37,6 +37,8 @@ struct PromptParams {
     int* status;
     int T, N, K;     // N: rows of y
     int inter;       // > 0: gate/up pair, N == inter
+    int glu_act;     // which gated pair (SHISO_GLU_*; 0: silu) ...
+    float glu_limit; // ... and its clamp
     int out_f32;
     int m_tiles, n_tiles;
     // SCALED, as in gemm_tcgen05_pair.cu: row t of x lacks the factor rsqrt(sum over c < scale_count
@@ -235,7 +237,7 @@ gemm_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     const int feature = n0 + c + 16 * q;
                     if (GLU) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) v[i] = silu_times(v[i], __uint_as_float(r[q + 2][i]) * row_scale);
+                        for (int i = 0; i < 16; ++i) v[i] = glu_times(v[i], __uint_as_float(r[q + 2][i]) * row_scale, p.glu_act, p.glu_limit);
                     } else if (p.bias) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -287,7 +289,8 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const PromptParams& p, 
 namespace {
 
 int run_prompt(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T, int N, int K, int inter,
-               const float* partials, int partial_count, int partial_stride, float eps, int sm_count, cudaStream_t stream) {
+               const float* partials, int partial_count, int partial_stride, float eps, int sm_count, cudaStream_t stream, int act = 0,
+             float limit = 0.0f) {
     if (T <= 0 || N <= 0) return SHISO_OK;
     if (K % 8 != 0 || K < 8 || N % 8 != 0) return SHISO_ERR_UNSUPPORTED;
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return SHISO_ERR_ALIGN;
@@ -301,6 +304,8 @@ int run_prompt(const void* x, const void* w, const float* bias, void* y, int y_d
     p.N = N;
     p.K = K;
     p.inter = inter;
+    p.glu_act = act;
+    p.glu_limit = limit;
     p.out_f32 = y_dtype == SHISO_F32 ? 1 : 0;
     p.m_tiles = (T + TILE_M - 1) / TILE_M;
     const int out_per_tile = inter > 0 ? TILE_N / 2 : TILE_N;
@@ -323,6 +328,13 @@ int run_prompt(const void* x, const void* w, const float* bias, void* y, int y_d
 SHISO_API int shiso_gemm_tcgen05_prompt(const void* x, const void* w, const float* bias, void* y, int y_dtype, int T,
                                         int N, int K, int inter, int sm_count, cudaStream_t stream) {
     return run_prompt(x, w, bias, y, y_dtype, T, N, K, inter, nullptr, 0, 0, 0.0f, sm_count, stream);
+}
+
+// The gate/up pair with another gated pair than silu (SHISO_GLU_* of common.cuh): w [2 * inter, K], y [T, inter].
+SHISO_API int shiso_gemm_tcgen05_prompt_glu(const void* x, const void* w, void* y, int y_dtype, int T, int inter, int K, int act,
+                                      float limit, int sm_count, cudaStream_t stream) {
+    if (inter <= 0 || act < SHISO_GLU_SILU || act > SHISO_GLU_SWISH_CLAMPED) return SHISO_ERR_SHAPE;
+    return run_prompt(x, w, nullptr, y, y_dtype, T, inter, K, inter, nullptr, 0, 0, 0.0f, sm_count, stream, act, limit);
 }
 
 // The same for rows x that lack their RMS scale (see PromptParams).

@@ -4,6 +4,7 @@
 // add_dyt_kernel:      x = residual (+ up to two block outputs), stored back; out = tanh(alpha x) * w + b.
 // stream_add_kernel:   out = residual + up to three blocks of rows (each float or bfloat16) + one vector
 //                      that is the same for every row; out may be the residual itself.
+// gate_rows_kernel:    x *= sigmoid(gate), entry by entry, in place.
 // glu_act_kernel:      the gated pair of a feed-forward over rows [gate | up]: silu(g) u, the tanh form
 //                      of gelu(g) u, or min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1).
 // joined_norm_store:   rows [q | k | (v) | ..]: one RMS norm over all query columns together and one
@@ -33,40 +34,87 @@ __device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i)
 
 // --------------------------------------------------------------------------- tanh norm
 
-// One thread per four neighbouring columns of a row (VEC) or per column.
-template <typename AT, bool VEC>
+// Loads and stores of N neighbouring entries at once (N = 1, 4 or 8 as the alignment allows).
+template <int N> __device__ __forceinline__ void load_n(const float* p, float* v) {
+    if constexpr (N == 1) {
+        v[0] = p[0];
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) {
+            const float4 q = *reinterpret_cast<const float4*>(p + i);
+            v[i] = q.x, v[i + 1] = q.y, v[i + 2] = q.z, v[i + 3] = q.w;
+        }
+    }
+}
+template <int N> __device__ __forceinline__ void load_n(const __nv_bfloat16* p, float* v) {
+    if constexpr (N == 1) {
+        v[0] = __bfloat162float(p[0]);
+    } else if constexpr (N == 4) {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&q.x), b = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
+        v[0] = __low2float(a), v[1] = __high2float(a), v[2] = __low2float(b), v[3] = __high2float(b);
+    } else {
+        const uint4 q = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+            v[2 * i] = __low2float(a), v[2 * i + 1] = __high2float(a);
+        }
+    }
+}
+template <int N> __device__ __forceinline__ void store_n(float* p, const float* v) {
+    if constexpr (N == 1) {
+        p[0] = v[0];
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+}
+template <int N> __device__ __forceinline__ void store_n(__nv_bfloat16* p, const float* v) {
+    if constexpr (N == 1) {
+        p[0] = __float2bfloat16_rn(v[0]);
+    } else {
+        uint32_t w[N / 2];
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&a);
+        }
+        if constexpr (N == 4) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+        else *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// One thread per N neighbouring columns of a row.
+template <typename AT, int N>
 __global__ void __launch_bounds__(256)
 add_dyt_kernel(float* __restrict__ residual, const AT* __restrict__ d0, const AT* __restrict__ d1, const int* __restrict__ rows,
                const float* __restrict__ w, const float* __restrict__ b, float alpha, AT* __restrict__ out, int out_rows, int hidden) {
     pdl_begin();
-    constexpr int N = VEC ? 4 : 1;
     const int per_row = hidden / N;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)out_rows * per_row) return;
     const int r = (int)(i / per_row), c = (int)(i % per_row) * N;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden + c;
-    float x[N];
-    if constexpr (VEC) {
-        const float4 v = *reinterpret_cast<const float4*>(residual + src);
-        x[0] = v.x, x[1] = v.y, x[2] = v.z, x[3] = v.w;
-    } else {
-        x[0] = residual[src];
-    }
+    float x[N], d[N], wv[N], bv[N];
+    load_n<N>(residual + src, x);
     if (d0) {
+        load_n<N>(d0 + src, d);
 #pragma unroll
-        for (int e = 0; e < N; ++e) x[e] += to_f32(d0[src + e]);
+        for (int e = 0; e < N; ++e) x[e] += d[e];
     }
     if (d1) {
+        load_n<N>(d1 + src, d);
 #pragma unroll
-        for (int e = 0; e < N; ++e) x[e] += to_f32(d1[src + e]);
+        for (int e = 0; e < N; ++e) x[e] += d[e];
     }
-    if (!rows && (d0 || d1)) {
-        if constexpr (VEC) *reinterpret_cast<float4*>(residual + src) = make_float4(x[0], x[1], x[2], x[3]);
-        else residual[src] = x[0];
-    }
-    AT* dst = out + (size_t)r * hidden + c;
+    if (!rows && (d0 || d1)) store_n<N>(residual + src, x);
+    load_n<N>(w + c, wv);
+    load_n<N>(b + c, bv);
 #pragma unroll
-    for (int e = 0; e < N; ++e) dst[e] = from_f32<AT>(tanhf(alpha * x[e]) * w[c + e] + b[c + e]);
+    for (int e = 0; e < N; ++e) x[e] = tanhf(alpha * x[e]) * wv[e] + bv[e];
+    store_n<N>(out + (size_t)r * hidden + c, x);
 }
 
 // residual float [T, hidden]; d0, d1: block outputs in the output type, or null; rows: the rows
@@ -74,18 +122,24 @@ add_dyt_kernel(float* __restrict__ residual, const AT* __restrict__ d0, const AT
 SHISO_API int shiso_add_dyt(float* residual, const void* d0, const void* d1, const int* rows, const float* w, const float* b,
                             float alpha, void* out, int out_dtype, int out_rows, int hidden, cudaStream_t stream) {
     if (out_rows <= 0 || hidden <= 0) return SHISO_OK;
-    const bool vec = hidden % 4 == 0 && (((uintptr_t)residual) & 15) == 0;
-    const unsigned blocks = ceil_div_u((long long)out_rows * (hidden / (vec ? 4 : 1)), 256);
-#define DYT_GO(AT)                                                                                                              \
-    {                                                                                                                           \
-        if (vec) launch_kernel(add_dyt_kernel<AT, true>, blocks, 256, 0, stream, residual, (const AT*)d0, (const AT*)d1, rows, w, b, alpha, (AT*)out, out_rows, hidden); \
-        else launch_kernel(add_dyt_kernel<AT, false>, blocks, 256, 0, stream, residual, (const AT*)d0, (const AT*)d1, rows, w, b, alpha, (AT*)out, out_rows, hidden);   \
-        return launch_status();                                                                                                 \
+    const bool aligned = ((((uintptr_t)residual) | ((uintptr_t)d0) | ((uintptr_t)d1) | ((uintptr_t)w) | ((uintptr_t)b) | ((uintptr_t)out)) & 15) == 0;
+    const int n = !aligned ? 1 : (out_dtype == SHISO_BF16 && hidden % 8 == 0) ? 8 : hidden % 4 == 0 ? 4 : 1;
+    const unsigned blocks = ceil_div_u((long long)out_rows * (hidden / n), 256);
+#define DYT_GO(AT, N)                                                                                                  \
+    launch_kernel(add_dyt_kernel<AT, N>, blocks, 256, 0, stream, residual, (const AT*)d0, (const AT*)d1, rows, w, b, alpha, \
+                  (AT*)out, out_rows, hidden)
+    if (out_dtype == SHISO_F32) {
+        if (n == 4) DYT_GO(float, 4);
+        else DYT_GO(float, 1);
+    } else if (out_dtype == SHISO_BF16) {
+        if (n == 8) DYT_GO(__nv_bfloat16, 8);
+        else if (n == 4) DYT_GO(__nv_bfloat16, 4);
+        else DYT_GO(__nv_bfloat16, 1);
+    } else {
+        return SHISO_ERR_DTYPE;
     }
-    if (out_dtype == SHISO_F32) DYT_GO(float)
-    if (out_dtype == SHISO_BF16) DYT_GO(__nv_bfloat16)
 #undef DYT_GO
-    return SHISO_ERR_DTYPE;
+    return launch_status();
 }
 
 // --------------------------------------------------------------------------- rows added to the stream
@@ -149,6 +203,48 @@ SHISO_API int shiso_glu_act(const void* gate_up, void* out, int act_dtype, int t
                       total, act, limit);
     else
         return SHISO_ERR_DTYPE;
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------- a gate per entry
+
+// x[t, c] *= sigmoid(gate[t, c]) in place; rows of x and of the gate have their own strides.
+template <typename AT, int N>
+__global__ void __launch_bounds__(256)
+gate_rows_kernel(AT* __restrict__ x, long long x_ld, const AT* __restrict__ gate, long long gate_ld, int tokens, int cols) {
+    pdl_begin();
+    const int per_row = cols / N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * per_row) return;
+    const int t = (int)(i / per_row), c = (int)(i % per_row) * N;
+    float v[N], g[N];
+    load_n<N>(x + (size_t)t * x_ld + c, v);
+    load_n<N>(gate + (size_t)t * gate_ld + c, g);
+#pragma unroll
+    for (int e = 0; e < N; ++e) v[e] *= 1.0f / (1.0f + expf(-g[e]));
+    store_n<N>(x + (size_t)t * x_ld + c, v);
+}
+
+SHISO_API int shiso_gate_rows(void* x, long long x_ld, const void* gate, long long gate_ld, int act_dtype, int tokens, int cols,
+                              cudaStream_t stream) {
+    if (tokens <= 0 || cols <= 0) return SHISO_OK;
+    if (act_dtype == SHISO_F32) {
+        const bool vec = cols % 4 == 0 && x_ld % 4 == 0 && gate_ld % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)gate)) & 15) == 0;
+        const unsigned blocks = ceil_div_u((long long)tokens * (cols / (vec ? 4 : 1)), 256);
+        if (vec) launch_kernel(gate_rows_kernel<float, 4>, blocks, 256, 0, stream, (float*)x, x_ld, (const float*)gate, gate_ld, tokens, cols);
+        else launch_kernel(gate_rows_kernel<float, 1>, blocks, 256, 0, stream, (float*)x, x_ld, (const float*)gate, gate_ld, tokens, cols);
+    } else if (act_dtype == SHISO_BF16) {
+        const bool vec = cols % 8 == 0 && x_ld % 8 == 0 && gate_ld % 8 == 0 && ((((uintptr_t)x) | ((uintptr_t)gate)) & 15) == 0;
+        const unsigned blocks = ceil_div_u((long long)tokens * (cols / (vec ? 8 : 1)), 256);
+        if (vec)
+            launch_kernel(gate_rows_kernel<__nv_bfloat16, 8>, blocks, 256, 0, stream, (__nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)gate,
+                          gate_ld, tokens, cols);
+        else
+            launch_kernel(gate_rows_kernel<__nv_bfloat16, 1>, blocks, 256, 0, stream, (__nv_bfloat16*)x, x_ld, (const __nv_bfloat16*)gate,
+                          gate_ld, tokens, cols);
+    } else {
+        return SHISO_ERR_DTYPE;
+    }
     return launch_status();
 }
 

@@ -90,6 +90,11 @@ _SIGNATURES = {
     "shiso_masked_attention_tiles": [P, LL, P, P, P, I, P, P, P, LL, P, LL, P, I, I, I, I, I, I, I, F, F, I, I, I, I, I, P],
     "shiso_norm_into": [P, P, I, P, P, I, I, F, P],
     "shiso_polynorm": [P, LL, I, P, P, I, I, F, P],
+    "shiso_gemm_stream_glu": [P, P, P, I, I, I, I, I, F, I, P],
+    "shiso_gemm_tcgen05_glu": [P, P, P, I, I, I, I, I, F, P],
+    "shiso_gemm_tcgen05_pair_glu": [P, P, P, I, I, I, I, I, F, I, P],
+    "shiso_gemm_tcgen05_prompt_glu": [P, P, P, I, I, I, I, I, F, I, P],
+    "shiso_gate_rows": [P, LL, P, LL, I, I, I, P],
     "shiso_embed_scaled": [P, P, P, P, I, P, I, I, I, F, P],
     "shiso_add_dyt": [P, P, P, P, P, P, F, P, I, I, I, P],
     "shiso_stream_add": [P, P, P, I, P, I, P, I, P, I, I, P],

@@ -444,11 +444,39 @@ def glu_act(gate_up: torch.Tensor, act: str, limit: float = 0.0) -> torch.Tensor
 
 
 def linear_glu(x: torch.Tensor, gate_up: torch.Tensor, out_dtype: torch.dtype, act: str, limit: float = 0.0) -> torch.Tensor:
-    """``act(x @ gate^T, x @ up^T)`` for ``gate_up = [gate; up]`` (the pairs of ``glu_act``).  The
-    silu pair takes ``linear_swiglu`` and its epilogues; the others run the product and then the
-    activation kernel."""
+    """``act(x @ gate^T, x @ up^T)`` for ``gate_up = [gate; up]`` (the pairs of ``glu_act``).  In
+    bfloat16 the pair is applied in the product's epilogue, by the kernels and at the sizes of
+    ``linear_swiglu`` (exponential and reciprocal from the special-function unit); other types run
+    the product and then the activation kernel."""
     if act == "silu":
         return linear_swiglu(x, gate_up, out_dtype)
+    if act not in _GLU_ACTS:
+        raise KernelError(f"gated pair {act!r}: expected one of {sorted(_GLU_ACTS)}")
+    _check(x, "x", None, 2)
+    _check(gate_up, "gate_up", None, 2)
+    tokens, k = x.shape
+    two_inter = gate_up.shape[0]
+    if two_inter % 2 or gate_up.shape[1] != k:
+        raise KernelError(f"gate/up matrix of shape {tuple(gate_up.shape)} does not fit rows of {k}")
+    inter, code = two_inter // 2, _GLU_ACTS[act]
+    lib = library()
+    if x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+        if tokens <= STREAM_KERNEL_MAX_TOKENS and k % 8 == 0:
+            out = torch.empty((tokens, inter), dtype=out_dtype, device=x.device)
+            status = lib.shiso_gemm_stream_glu(_ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, inter, k, code, float(limit),
+                                               _sm_count(), _stream())
+            _done(status, f"linear_glu {act} (streaming)", shape=(tokens, two_inter, k))
+            return out
+        if lib.shiso_gemm_tcgen05_supported(k, _ptr(x), _ptr(gate_up)):
+            out = torch.empty((tokens, inter), dtype=out_dtype, device=x.device)
+            if tokens >= PROMPT_MIN_TOKENS and inter % 8 == 0:
+                product = lib.shiso_gemm_tcgen05_pair_glu if tokens >= PAIR_MIN_TOKENS_GLU else lib.shiso_gemm_tcgen05_prompt_glu
+                status = product(_ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, inter, k, code, float(limit), _sm_count(), _stream())
+                _done(status, f"linear_glu {act} (tcgen05, persistent)", shape=(tokens, two_inter, k))
+                return out
+            status = lib.shiso_gemm_tcgen05_glu(_ptr(x), _ptr(gate_up), _ptr(out), _code(out), tokens, inter, k, code, float(limit), _stream())
+            _done(status, f"linear_glu {act} (tcgen05)", shape=(tokens, two_inter, k))
+            return out
     return glu_act(linear(x, gate_up, out_dtype), act, limit)
 
 
@@ -1224,6 +1252,7 @@ _HEAD_NORMS = {None: 0, "before": 1, "after": 2}
 _MASKS = {"window": 0, "chunk": 1}
 MASKED_MAX_HEAD_DIM = 256  # what the kernels of this group keep of a head in a warp's registers
 MASKED_MAX_SPLITS = 16  # CTAs that share a (row, head)'s keys in the general kernel
+NO_WINDOW = 1 << 30  # a window of this size or more reaches back to the start of any sequence: the kernels that know "no window" are told so
 MASKED_SCRATCH_BYTES = 64 << 20  # their partial results, at most; larger steps take one CTA a (row, head)
 
 
@@ -1265,6 +1294,17 @@ def head_prepare_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, norm_ord
     )
     _done(status, "head_prepare_store", shape=(proj.shape[0], heads + kv_heads, dim))
     return proj[:, :q_cols]
+
+
+def gate_rows(x, gate):
+    """``x *= sigmoid(gate)`` entry by entry, in place; both ``[T, C]`` in one type (column ranges may be given).  Returns ``x``."""
+    x_ld = _rows(x, "rows", None)
+    gate_ld = _rows(gate, "gate", x.dtype, x.shape[1])
+    if gate.shape[0] != x.shape[0]:
+        raise KernelError(f"{gate.shape[0]} gate rows for {x.shape[0]} rows")
+    status = library().shiso_gate_rows(x.data_ptr(), x_ld, gate.data_ptr(), gate_ld, _code(x), x.shape[0], x.shape[1], _stream())
+    _done(status, "gate_rows", shape=tuple(x.shape))
+    return x
 
 
 def joined_norm_store(proj, heads, kv_heads, dim, vdim, q_w, k_w, eps, q_temperature, values_from_keys, step, k_cache, v_cache,
@@ -1335,8 +1375,9 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
     # A softmax over a window (with or without kept first tokens), heads of 64, no cap and no gate is
     # what the framework's tensor-memory prompt kernel and its TMA decode kernel compute: they take
     # the first positions as tiles of their own ahead of the window's.
+    # (A gate per output entry is applied behind them by a row kernel; a gate per head keeps the kernels that know it.)
     plain_window = (
-        not general and act == torch.bfloat16 and mask == "window" and not sigmoid and not softcap and gate is None
+        not general and act == torch.bfloat16 and mask == "window" and not sigmoid and not softcap and (gate is None or wide)
         and dim == vdim and q.data_ptr() % 16 == 0 and q_ld % 8 == 0
     )
     if (
@@ -1346,11 +1387,11 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
         splits = decode_splits(tokens, kv_heads, min(block_table.shape[1] * page_size, size + keep_first + 2 * 64), True)
         status = lib.shiso_decode_attention_fused_kept(
             q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
-            _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, dim, page_size, k_cache.shape[0], float(scale), int(size),
-            int(keep_first), splits, _stream(),
+            _ptr(step.seq_of_token), _ptr(out), tokens, heads, kv_heads, dim, page_size, k_cache.shape[0], float(scale),
+            0 if size >= NO_WINDOW else int(size), int(keep_first), splits, _stream(),
         )
         _done(status, f"decode_attention (fused) {what}", shape=(tokens, heads, dim))
-        return out
+        return gate_rows(out, gate) if wide else out
     if (
         plain_window and not getattr(step, "all_decode", False) and tokens >= TC_ATTENTION_MIN_TOKENS
         and getattr(step, "max_q_len", tokens) >= TC_ATTENTION_MIN_PORTION
@@ -1364,10 +1405,10 @@ def masked_attention(q, heads, k_cache, v_cache, block_table, page_size, scale, 
         status = lib.shiso_prefill_attention_tc_kept(
             q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
             _ptr(step.start_pos), _ptr(out), heads * vdim, tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
-            k_cache.shape[0], float(scale), int(size), int(keep_first), _stream(),
+            k_cache.shape[0], float(scale), 0 if size >= NO_WINDOW else int(size), int(keep_first), _stream(),
         )
         _done(status, f"prefill_attention (tcgen05) {what}", shape=(tokens, heads, dim))
-        return out
+        return gate_rows(out, gate) if wide else out
     if (
         not general and act == torch.bfloat16 and not getattr(step, "all_decode", False)
         and lib.shiso_masked_attention_tiles_supported(dim, vdim)

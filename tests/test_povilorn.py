@@ -654,3 +654,39 @@ def test_the_scaled_embedding(backend):
     ids = torch.tensor([3, 19, 0, 3], dtype=torch.int32, device=env.device)
     got = env.ops.embed(ids, table, scale=3.0)
     assert got.dtype == torch.float32 and torch.equal(got.cpu(), table.float().cpu()[[3, 19, 0, 3]] * 3.0)  # exact: the product is formed in float32
+
+
+@pytest.mark.gpu
+def test_gated_pairs_in_the_products_epilogues():
+    """Every route of a gate/up product (a handful of rows, up to 192, the persistent kernels on one
+    SM and on pairs) with each gated pair against the plain one, at sizes with ragged last tiles."""
+    env = build_env("cuda", torch.bfloat16)
+    g = torch.Generator().manual_seed(12)
+    for k, inter in ((256, 384), (200, 72), (1024, 1416)):
+        w = (torch.randn(2 * inter, k, generator=g) * 0.08).to(env.device, torch.bfloat16)
+        for rows in (1, 8, 9, 70, 192, 200, 511, 520, 1100):
+            x = torch.randn(rows, k, generator=g).to(env.device, torch.bfloat16)
+            for act, limit in (("gelu_tanh", 0.0), ("swish_clamped", 0.7), ("swish_clamped", 6.0), ("silu", 0.0)):
+                got = env.ops.linear_glu(x, w, torch.bfloat16, act, limit).double().cpu()
+                want = fake_kernels.linear_glu(x.cpu(), w.cpu(), torch.float64, act, limit)
+                close(got, want, torch.bfloat16, f"{act} {limit}: {rows} x {2 * inter} x {k}")
+        x = torch.randn(33, k, generator=g).to(env.device)
+        got = env.ops.linear_glu(x, w.float(), torch.float32, "gelu_tanh", 0.0).double().cpu()
+        close(got, fake_kernels.linear_glu(x.cpu(), w.float().cpu(), torch.float64, "gelu_tanh", 0.0), torch.float32, f"float32 gelu {k}")
+
+
+@pytest.mark.gpu
+def test_a_gate_per_entry_behind_the_fast_attention_kernels():
+    """``gate_rows`` alone, on column ranges of wider rows, in both types and at widths no vector divides."""
+    for dtype in (torch.float32, torch.bfloat16):
+        env = build_env("cuda", dtype)
+        g = torch.Generator().manual_seed(13)
+        for tokens, cols, pad in ((5, 64, 0), (3, 50, 6), (70, 384, 128)):
+            rows = torch.randn(tokens, cols + pad, generator=g).to(env.device, dtype)
+            gates = torch.randn(tokens, cols + 2 * pad, generator=g).to(env.device, dtype)
+            x, gate = rows[:, :cols], gates[:, pad : pad + cols]
+            want = x.double().cpu() * torch.sigmoid(gate.double().cpu())
+            untouched = rows[:, cols:].clone()
+            got = env.ops.gate_rows(x, gate)
+            close(got.double().cpu(), want, dtype, f"gate rows {tokens} x {cols}")
+            assert torch.equal(rows[:, cols:], untouched)
