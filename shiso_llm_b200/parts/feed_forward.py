@@ -210,7 +210,9 @@ class RoutedExperts(FeedForward):
             gate = tensors[self.shared_gate_name]
             if gate.dtype != self.router.dtype:
                 gate, self.router = gate.float(), self.router.float()
-            self.router = torch.cat([self.router, gate], dim=0).contiguous()
+            # (rows up to a multiple of eight are zeros: the tensor-memory products for long portions take such matrices)
+            pad = torch.zeros((-(self.experts + 1) % 8, self.hidden), dtype=gate.dtype, device=gate.device)
+            self.router = torch.cat([self.router, gate, pad], dim=0).contiguous()
         self.correction = tensors[self.correction_name] if self.correction_name is not None else None
         mats = [tensors[n[k]] for n in self.expert_names for k in ("gate", "up", "down")]
         wide = len({m.dtype for m in mats}) > 1
@@ -239,7 +241,7 @@ class RoutedExperts(FeedForward):
         if self.activation != "silu":
             more["act"], more["limit"] = self.activation, self.limit
         if self.shared_gate_name is not None:
-            more["extra_gate"] = logits[:, self.experts :]  # [T, 1] float32 logits
+            more["extra_gate"] = logits[:, self.experts : self.experts + 1]  # [T, 1] float32 logits
         if self.identity:
             more["identity"] = self.identity
         return ops.routed_experts(x, ids, weights, self.gate_up, self.down, extra, **more)
