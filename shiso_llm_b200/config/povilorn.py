@@ -95,8 +95,8 @@ class PovilornConfig:
         loop = None
         if document.get("loop") is not None:
             loop = (_int(document, "loop.start", 0), _int(document, "loop.stop", 0), _int(document, "loop.times", 1))
-            if not loop[0] < loop[1] <= len(layers):
-                raise InvalidValue("loop", document["loop"], f"start < stop <= {len(layers)} layers is needed")
+            if not loop[0] <= loop[1] <= len(layers):
+                raise InvalidValue("loop", document["loop"], f"start <= stop <= {len(layers)} layers is needed")
         return cls(vocab=vocab, width=width, eps=eps, layers=tuple(copy.deepcopy(layers)), embedding_scale=scale, loop=loop)
 
     @staticmethod
@@ -169,7 +169,7 @@ class PovilornConfig:
         """``(layer, pass)`` in running order: ``pass`` is the number of the pass that begins with
         this run of the layer, or None."""
         n = len(self.layers)
-        if self.loop is None:
+        if self.loop is None or self.loop[0] == self.loop[1]:  # (a stretch without layers has no pass to begin)
             return [(i, None) for i in range(n)]
         start, stop, times = self.loop
         order = [(i, None) for i in range(start)]
@@ -253,7 +253,7 @@ def build_plan(config: PovilornConfig) -> ModelPlan:
     )
     unused = tuple(name for i, layer in enumerate(config.layers) if layer.get("mlp") is None
                    for name in (f"l{i}.norm2", f"l{i}.norm2.alpha", f"l{i}.norm2.b"))
-    if config.loop is None:
+    if not any(entry.add_vector is not None for entry in order):
         unused += (LOOP_VECTORS,)
     return ModelPlan(
         architecture=ARCHITECTURE,

@@ -252,7 +252,9 @@ SHISO_API int shiso_gate_rows(void* x, long long x_ld, const void* gate, long lo
 
 // One block per row.  Columns [0, q_cols) are the queries, [q_cols, q_cols + k_cols) the keys,
 // v_cols columns from v_col on the values (v_col = q_cols when the values are the keys as they came).
-template <typename AT>
+// A thread takes N neighbouring columns at a time (N > 1: every extent and stride is a multiple of N
+// and every pointer 16-byte aligned); the order of a row's sums depends on the block's size only.
+template <typename AT, int N>
 __global__ void __launch_bounds__(256)
 joined_norm_store_kernel(AT* __restrict__ proj, long long ld, int q_cols, int k_cols, int v_col, int v_cols, const float* __restrict__ q_w,
                          const float* __restrict__ k_w, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -263,14 +265,18 @@ joined_norm_store_kernel(AT* __restrict__ proj, long long ld, int q_cols, int k_
     const int t = blockIdx.x;
     AT* row = proj + (size_t)t * ld;
     const int pos = positions[t];
+    const int first = threadIdx.x * N, stride = blockDim.x * N;
+    float v[N], w[N];
     float sq = 0.0f, sk = 0.0f;
-    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) {
-        const float v = to_f32(row[i]);
-        sq += v * v;
+    for (int i = first; i < q_cols; i += stride) {
+        load_n<N>(row + i, v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) sq += v[e] * v[e];
     }
-    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
-        const float v = to_f32(row[q_cols + i]);
-        sk += v * v;
+    for (int i = first; i < k_cols; i += stride) {
+        load_n<N>(row + q_cols + i, v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) sk += v[e] * v[e];
     }
     float q_inv = rsqrtf(block_sum(sq, scratch) / (float)q_cols + eps);
     const float k_inv = rsqrtf(block_sum(sk, scratch) / (float)k_cols + eps);
@@ -280,10 +286,25 @@ joined_norm_store_kernel(AT* __restrict__ proj, long long ld, int q_cols, int k_
         const size_t at = (size_t)page * page_size + pos % page_size;
         AT* k_dst = k_cache + at * k_cols;
         AT* v_dst = v_cache + at * v_cols;
-        for (int i = threadIdx.x; i < k_cols; i += blockDim.x) k_dst[i] = from_f32<AT>(to_f32(row[q_cols + i]) * k_inv * k_w[i]);
-        for (int i = threadIdx.x; i < v_cols; i += blockDim.x) v_dst[i] = row[v_col + i];
+        for (int i = first; i < k_cols; i += stride) {
+            load_n<N>(row + q_cols + i, v);
+            load_n<N>(k_w + i, w);
+#pragma unroll
+            for (int e = 0; e < N; ++e) v[e] = v[e] * k_inv * w[e];
+            store_n<N>(k_dst + i, v);
+        }
+        for (int i = first; i < v_cols; i += stride) {  // the values as they stand: a copy
+            load_n<N>(row + v_col + i, v);
+            store_n<N>(v_dst + i, v);
+        }
     }
-    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) row[i] = from_f32<AT>(to_f32(row[i]) * q_inv * q_w[i]);
+    for (int i = first; i < q_cols; i += stride) {
+        load_n<N>(row + i, v);
+        load_n<N>(q_w + i, w);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v[e] = v[e] * q_inv * w[e];
+        store_n<N>(row + i, v);
+    }
 }
 
 SHISO_API int shiso_joined_norm_store(void* proj, long long ld, int act_dtype, int q_cols, int k_cols, int v_col, int v_cols,
@@ -292,16 +313,22 @@ SHISO_API int shiso_joined_norm_store(void* proj, long long ld, int act_dtype, i
                                       float eps, float temp_coef, int temp_every, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (q_cols <= 0 || k_cols <= 0 || v_cols <= 0 || v_col < q_cols || page_size <= 0 || temp_every < 0) return SHISO_ERR_SHAPE;
-    const int threads = q_cols >= 1024 ? 256 : 128;
-    if (act_dtype == SHISO_F32)
-        launch_kernel(joined_norm_store_kernel<float>, tokens, threads, 0, stream, (float*)proj, ld, q_cols, k_cols, v_col, v_cols, q_w,
-                      k_w, positions, seq_of_token, table, table_width, (float*)k_cache, (float*)v_cache, page_size, eps, temp_coef,
-                      temp_every);
-    else if (act_dtype == SHISO_BF16)
-        launch_kernel(joined_norm_store_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (__nv_bfloat16*)proj, ld, q_cols, k_cols,
-                      v_col, v_cols, q_w, k_w, positions, seq_of_token, table, table_width, (__nv_bfloat16*)k_cache,
-                      (__nv_bfloat16*)v_cache, page_size, eps, temp_coef, temp_every);
-    else
+    const int n = act_dtype == SHISO_BF16 ? 8 : 4;
+    const bool wide = q_cols % n == 0 && k_cols % n == 0 && v_col % n == 0 && v_cols % n == 0 && ld % n == 0 &&
+                      ((((uintptr_t)proj) | ((uintptr_t)q_w) | ((uintptr_t)k_w) | ((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) == 0;
+    const int threads = q_cols >= (wide ? 1024 * n / 2 : 1024) ? 256 : 128;
+#define JOINED_GO(AT, N)                                                                                                       \
+    launch_kernel(joined_norm_store_kernel<AT, N>, tokens, threads, 0, stream, (AT*)proj, ld, q_cols, k_cols, v_col, v_cols, q_w, k_w, \
+                  positions, seq_of_token, table, table_width, (AT*)k_cache, (AT*)v_cache, page_size, eps, temp_coef, temp_every)
+    if (act_dtype == SHISO_F32) {
+        if (wide) JOINED_GO(float, 4);
+        else JOINED_GO(float, 1);
+    } else if (act_dtype == SHISO_BF16) {
+        if (wide) JOINED_GO(__nv_bfloat16, 8);
+        else JOINED_GO(__nv_bfloat16, 1);
+    } else {
         return SHISO_ERR_DTYPE;
+    }
+#undef JOINED_GO
     return launch_status();
 }

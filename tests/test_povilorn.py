@@ -151,6 +151,11 @@ def test_configuration_is_read_from_its_own_keys():
     assert [(e.layer, e.add_first, e.add_vector) for e in plan_b.order] == [(i, False, None) for i in range(4)]
     assert plan_b.layers[0].mixer.params["q_temperature"] is None and plan_b.layers[0].feed_forward.params["shared"] is None
     assert [e.add_vector for e in plan_from_document(DOC_D)[2].order] == [None, ("loop.step", 0)]
+    # a stretch without layers: nothing repeats, nothing is added, and a file may still hold the vectors
+    empty = copy.deepcopy(DOC_D)
+    empty["loop"] = {"start": 1, "stop": 1, "times": 3}
+    plan_e = plan_from_document(empty)[2]
+    assert [(e.layer, e.add_first, e.add_vector) for e in plan_e.order] == [(0, False, None), (1, False, None)] and "loop.step" in plan_e.unused_tensors
 
 
 def test_configuration_refusals():
@@ -174,7 +179,7 @@ def test_configuration_refusals():
         (("layers", 0, "mixer", "rot", "dims"), 3), (("layers", 0, "mixer", "rot", "dims"), 6), (("layers", 1, "mixer", "q_temp", "every"), 0),
         (("layers", 1, "mlp", "router", "top"), 10), (("layers", 1, "mlp", "router", "groups", "count"), 4),
         (("layers", 1, "mlp", "router", "groups", "keep"), 4), (("layers", 1, "mlp", "expert", "limit"), 0.0),
-        (("layers", 0, "mlp", "kind"), "glu"), (("loop", "stop"), 5), (("loop", "start"), 3), (("vocab",), 0), (("layers",), []),
+        (("layers", 0, "mlp", "kind"), "glu"), (("loop", "stop"), 5), (("loop", "start"), 4), (("vocab",), 0), (("layers",), []),
     ]:
         with pytest.raises(InvalidValue):
             PovilornConfig.from_dict(changed(path, value))
