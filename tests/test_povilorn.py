@@ -306,8 +306,8 @@ DOC_WIDE = {
     "architecture": "Povilorn", "vocab": 400, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.5},
     "loop": {"start": 1, "stop": 3, "times": 2},
     "layers": [
-        layer("attention", attention(4, 2, 64, 0.125, 0.2, 128), dense(160)),
-        layer("latent_attention", latent(4, 32, 32, 48, 64, 0.11, 32, 10000.0, (8.0, 128, 16.0, 1.0)), moe(6, 2, 2, 4, 3, 64, 1.0, (96, 1.5))),
+        layer("attention", attention(4, 2, 64, 0.11, 0.2, 200), dense(160)),
+        layer("latent_attention", latent(3, 32, 32, 48, 64, 0.11, 32, 10000.0, (6.0, 128, 16.0, 1.0)), moe(6, 2, 2, 4, 2, 64, 1.25, (80, 2.0))),
         layer("attention", attention(2, 1, 128, 0.09, 0.3, 300), None),
         layer("latent_attention", latent(2, 64, 16, 128, 96, 0.1, 8, 300.0), dense(96)),
     ],
